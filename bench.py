@@ -1,0 +1,381 @@
+"""Benchmark of the 2:4 sparse path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the hot path over one batch of synthetic input: the tcgen05 sparse
+GEMM C = A24 . B at M = K = N = 8192, fp16, A pre-compressed (the configuration the
+headline metric is quoted on).  With N > 1 ranks (torchrun, one per GPU) every rank
+multiplies the same compressed A by its own 8192-column shard of B: the output columns
+are sharded, no collective is on the data path, per-GPU work is fixed (weak scaling).
+
+Printed by rank 0, one JSON line:
+  value      whole-job dense-equivalent TFLOP/s (2 M N K per GEMM, the reference's
+             convention, compression/dev/8.11_benchmark_2_kernel.py:49-50), inputs resident in HBM
+  e2e        same metric through the reference-facing call run_sparse_ws_matmul(A, E, B)
+             with pinned HOST buffers: H2D of A values, E and B and D2H of C inside the timed region
+  roofline   the GEMM kernel against 2 x the measured dense bf16 tensor peak
+  prune_compress   the standalone fused prune+compress kernel at 16384 x 16384 fp16 in GB/s
+             (3.125 bytes per element, compression/dev/8.11.1_benchmark_pruning.py:43-52)
+             with its HBM roofline
+  cpu_baseline     the CPU port of the reference path timed on this box's host cores on a
+             bounded sample (rank 0, N = 1 only)
+
+`--impl reference` times the reference's CPU path instead (its torch functions cannot
+travel to the GPU box, so this is the oracle's C port of prune_2_4 +
+compress_dense_to_sparse plus a torch fp32 CPU matmul, which is what the reference's
+`A_pruned @ B` runs on a CPU).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+PKG = ROOT / "gpu-compression-kernel_b200"
+for p in (str(ROOT), str(PKG), str(PKG / "compression")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+GEMM_M = GEMM_K = GEMM_N = 8192
+PC_M = PC_K = 16384
+H100_PRECOMPRESSED_SPARSE_8192 = 1015.48   # TFLOP/s, the reference's published number for this metric (H100)
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.tmp = None
+
+    def start(self):
+        try:
+            self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [r.split(",") for r in Path(self.tmp.name).read_text().splitlines() if r.strip()]
+        os.unlink(self.tmp.name)
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        if sm:
+            # under load = the upper half of the samples (idle samples before / after pull the median down)
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def time_steps(fn, steps, stream):
+    """device time of `steps` back-to-back calls, CUDA events on the launching stream"""
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    stop.record(stream)
+    stop.synchronize()
+    return start.elapsed_time(stop)  # ms
+
+
+# ---------------------------------------------------------------------------- CPU baseline
+
+def cpu_reference_sample(rows: int, threads: int):
+    """The reference's CPU path on a row slab of the GEMM workload:
+    prune_2_4 + compress_dense_to_sparse (C port) then A_pruned.float() @ B.float() (torch)."""
+    import oracle
+    oracle.set_num_threads(threads)
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(4000)
+    A = torch.randn(rows, GEMM_K, generator=g).to(torch.float16)
+    B = torch.randn(GEMM_K, GEMM_N, generator=g).to(torch.float16)
+    a_bits = A.view(torch.int16).numpy().view(np.uint16)
+    Bf = B.float()
+
+    def step():
+        t0 = time.perf_counter()
+        pruned = oracle.prune(a_bits, oracle.FP16)
+        oracle.compress(pruned, oracle.FP16)
+        t1 = time.perf_counter()
+        Ap = torch.from_numpy(pruned.view(np.int16)).view(torch.float16).float()
+        C = (Ap @ Bf).to(torch.float16)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1, C
+
+    return step
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return 0
+    threads = os.cpu_count() or 1
+    rows = 512
+    step = cpu_reference_sample(rows, threads)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t_pc = t_mm = 0.0
+    for _ in range(args.steps):
+        a, b, _ = step()
+        t_pc += a
+        t_mm += b
+    t_pc /= args.steps
+    t_mm /= args.steps
+    flops = 2.0 * rows * GEMM_N * GEMM_K
+    value = flops / t_mm / 1e12
+    sample = (f"first {rows} of {GEMM_M} rows of A against the full {GEMM_K}x{GEMM_N} B: C-port prune+compress "
+              f"({3.125 * rows * GEMM_K / t_pc / 1e9:.3f} GB/s) then torch fp32 matmul; matmul time only in value")
+    line = {
+        "impl": "reference", "metric": "sparse_gemm_dense_equiv_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": (t_pc + t_mm) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"sparse GEMM M=K=N={GEMM_M} fp16, A 2:4 pre-compressed, fp32 accumulate"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample,
+                         "prune_compress_gbs": 3.125 * rows * GEMM_K / t_pc / 1e9},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------- GPU arm
+
+def run_ours(args, rank, world, local):
+    import s24
+    from s24 import _lib
+    import gluon_ws_sparse
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.current_stream(dev)
+    peaks = measured_peaks()
+
+    # ---- inputs (seeded, N(0,1) like every reference benchmark: 8.11_benchmark_2_kernel.py:67-68)
+    g = torch.Generator(device=dev).manual_seed(4000)
+    A = torch.randn(GEMM_M, GEMM_K, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    gb = torch.Generator(device=dev).manual_seed(4100 + rank)          # each rank owns a different column shard of B
+    B = torch.randn(GEMM_K, GEMM_N, generator=gb, device=dev, dtype=torch.float32).to(torch.float16)
+    vals, E, tc = s24.prune_compress(A, want_ref=True, want_tc=True)
+    C = torch.empty(GEMM_M, GEMM_N, dtype=torch.float16, device=dev)
+    del A
+
+    def gemm_step():
+        s24.spmm(vals, tc, B, out=C)
+
+    def barrier():
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        gemm_step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    ms = time_steps(gemm_step, args.steps, stream)
+    barrier()
+    rc = _lib.lib().s24_device_status(None)
+    if rc != 0:
+        raise SystemExit(f"device status after the timed region: {_lib.last_error()}")
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if use_dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    ms_per_step = ms_max / args.steps
+    flops_per_step = 2.0 * GEMM_M * GEMM_N * GEMM_K * world
+    value = flops_per_step / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the reference-facing call with host buffers (every rank, max over ranks)
+    h_vals = vals.cpu().pin_memory()
+    h_E = E.cpu().pin_memory()
+    h_B = B.cpu().pin_memory()
+    h_C = torch.empty(GEMM_M, GEMM_N, dtype=torch.float16).pin_memory()
+    d_vals, d_E, d_B = torch.empty_like(vals), torch.empty_like(E), torch.empty_like(B)
+
+    def e2e_step():
+        d_vals.copy_(h_vals, non_blocking=True)
+        d_E.copy_(h_E, non_blocking=True)
+        d_B.copy_(h_B, non_blocking=True)
+        out = gluon_ws_sparse.run_sparse_ws_matmul(d_vals, d_E, d_B)
+        h_C.copy_(out, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ms_e2e = time_steps(e2e_step, e2e_steps, stream)
+    barrier()
+    t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
+    if use_dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = flops_per_step / (float(t.item()) / e2e_steps * 1e-3) / 1e12
+    h2d = (h_vals.numel() + h_B.numel()) * 2 + h_E.numel() * 2
+    d2h = h_C.numel() * 2
+    if rank == 0:
+        clocks = sampler.stop()
+    del h_vals, h_E, h_B, h_C, d_vals, d_E, d_B
+
+    # ---- standalone prune+compress bandwidth (rank 0 reports its own GPU)
+    pc = None
+    if rank == 0:
+        gp = torch.Generator(device=dev).manual_seed(2014)
+        Ap = torch.randn(PC_M, PC_K, generator=gp, device=dev, dtype=torch.float32).to(torch.float16)
+        pv = torch.empty(PC_M, PC_K // 2, dtype=torch.float16, device=dev)
+        pe = torch.empty(PC_M // 16, PC_K, dtype=torch.int16, device=dev)
+        L = _lib.lib()
+        import ctypes
+        sp = ctypes.c_void_p(stream.cuda_stream)
+
+        def pc_step():
+            _lib.check(L.s24_prune_compress(ctypes.c_void_p(Ap.data_ptr()), PC_M, PC_K, PC_K, _lib.FP16,
+                                            _lib.MODE_SIGNED, _lib.TIE_REFERENCE, ctypes.c_void_p(pv.data_ptr()),
+                                            ctypes.c_void_p(pe.data_ptr()), None, sp))
+
+        for _ in range(5):
+            pc_step()
+        torch.cuda.synchronize(dev)
+        pc_steps = 20
+        ms_pc = time_steps(pc_step, pc_steps, stream) / pc_steps
+        bytes_pc = 3.125 * PC_M * PC_K
+        gbs = bytes_pc / (ms_pc * 1e-3) / 1e9
+        pc = {"metric": "prune_compress_gbs", "value": gbs, "unit": "GB/s", "ms": ms_pc,
+              "workload": f"fused prune+compress fp16 {PC_M}x{PC_K} -> values + reference-layout metadata",
+              "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                           "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                           "frac_of_nominal_8TBs": gbs / 8000.0}}
+        del Ap, pv, pe
+
+    # ---- CPU baseline (rank 0, single GPU run only; bounded sample)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        rows = 512
+        step = cpu_reference_sample(rows, threads)
+        step()
+        reps, t_pc, t_mm = 3, 0.0, 0.0
+        for _ in range(reps):
+            a, b, _ = step()
+            t_pc += a / reps
+            t_mm += b / reps
+        cpu = {"value": 2.0 * rows * GEMM_N * GEMM_K / t_mm / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"first {rows} of {GEMM_M} rows of A against the full B: C-port prune+compress then torch fp32 "
+                         f"CPU matmul (matmul time in value)",
+               "prune_compress_gbs": 3.125 * rows * GEMM_K / t_pc / 1e9}
+
+    if rank == 0:
+        sparse_peak = 2.0 * peaks["bf16_tflops"]
+        per_gpu = value / world
+        line = {
+            "metric": "sparse_gemm_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": value / world / H100_PRECOMPRESSED_SPARSE_8192 if world == 1 else None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"sparse GEMM M=K=N={GEMM_M} fp16, A 2:4 pre-compressed, fp32 accumulate, fp16 out; "
+                                   f"per GPU one {GEMM_K}x{GEMM_N} column shard of B",
+                       "parallelism": f"N-sharded x{world}, no data-path collective",
+                       "l2": "operands + output (328 MB per GPU) exceed the 126 MB L2; no explicit flush",
+                       "sparse_issued_tflops": value / 2.0,
+                       "baseline_note": "vs_baseline divides by the reference's published H100 number (1015.48 TFLOP/s)"},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": sparse_peak, "unit": "TFLOP/s",
+                         "frac": per_gpu / sparse_peak, "traffic": None, "peak_source": peaks["source"],
+                         "peak_note": "2 x measured dense bf16 burst peak (2:4 sparse issues half the MACs)",
+                         "frac_of_sustained": per_gpu / (2.0 * peaks["bf16_tflops_sustained"])},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "call": "run_sparse_ws_matmul(A_vals, E, B) with pinned host buffers"},
+            "gpu_launches": args.steps * world,
+            "clocks": clocks,
+        }
+        if pc is not None:
+            line["prune_compress"] = pc
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if use_dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    if args.impl == "reference":
+        return run_reference_arm(args, rank, world)
+    if world == 1 and args.gpus > 1:
+        # launched without torchrun: re-launch one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29511", __file__, "--gpus", str(args.gpus),
+               "--steps", str(args.steps), "--warmup", str(args.warmup)] + (["--no-cpu"] if args.no_cpu else [])
+        return subprocess.call(cmd)
+    return run_ours(args, rank, world, local)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,323 @@
+// prune_compress.cu -- bandwidth-bound kernels: 2:4 prune, compress, fused prune+compress
+// and metadata layout conversion.
+//
+// Replaces the GPU work behind the reference's prune_2_4 (compression/prune.py:57-96),
+// compress_dense_to_sparse (compression/compress_2_4.py:32-161) and its standalone fused
+// kernel ws_tma_compress_2_4_kernel (compression/kernels/11.1_2_kernel_baseline.py:171-203).
+//
+// Fused kernel layout.  One warp owns a 16-row x 128-column block of A.  Lane
+// (m0 = lane/4, jj = lane%4) reads rows m0 and m0+8 of the block, 32 consecutive
+// elements each (64 bytes per row, two 256-bit loads), so a warp-wide load covers whole
+// 128-byte lines.  All ranking happens in registers of the owning lane -- no shared memory,
+// no shuffles -- and the choice of rows (r, r+8) and 32-column spans makes every output
+// store a full-line store:
+//   * values:   32 bytes per row per lane, 4 lanes = one 128-byte line;
+//   * metadata, reference layout: the lane holds two adjacent 32-bit words of the
+//     reordered buffer, the warp writes two full 128-byte lines;
+//   * metadata, tensor-core layout: lane index == word index within a 128-byte line.
+// Algorithmic traffic: 2 bytes read + 1 byte of values + 1/8 byte of metadata per element
+// (plus another 1/8 if both metadata layouts are requested).
+#include "s24_common.cuh"
+#include "prune_core.cuh"
+
+namespace s24 {
+
+__device__ __forceinline__ void ld256(const void* p, uint32_t (&r)[8])
+{
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+
+__device__ __forceinline__ void ld128x2(const void* p, uint32_t (&r)[8])
+{
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(static_cast<const char*>(p) + 16));
+}
+
+__device__ __forceinline__ void st256(void* p, const uint32_t (&r)[8])
+{
+    asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+struct PcParams {
+    const uint16_t* A;
+    int64_t lda;       // elements
+    int64_t M, K;
+    uint16_t* vals;    // (M, K/2)
+    uint32_t* meta_ref;  // (M/16, K/2) words, may be null
+    uint32_t* meta_tc;   // records, may be null
+    int mode, tie;
+    uint32_t keymask, force_keep, keep_zero_bits;
+    int64_t col_blocks;  // ceil(K / 128)
+    int64_t warp_tiles;  // (M/16) * col_blocks
+};
+
+// 32 elements of one row -> 16 stored values + 32 metadata bits
+template <int DT>
+__device__ __forceinline__ uint32_t row_span(const uint32_t (&lo)[8], const uint32_t (&hi)[8], const PcParams& p,
+                                             uint32_t (&out)[8])
+{
+    uint32_t c0 = prune_compress_8<DT>(lo[0], lo[1], lo[2], lo[3], p.mode, p.tie, p.keymask, p.force_keep,
+                                       p.keep_zero_bits, out[0], out[1]);
+    uint32_t c1 = prune_compress_8<DT>(lo[4], lo[5], lo[6], lo[7], p.mode, p.tie, p.keymask, p.force_keep,
+                                       p.keep_zero_bits, out[2], out[3]);
+    uint32_t c2 = prune_compress_8<DT>(hi[0], hi[1], hi[2], hi[3], p.mode, p.tie, p.keymask, p.force_keep,
+                                       p.keep_zero_bits, out[4], out[5]);
+    uint32_t c3 = prune_compress_8<DT>(hi[4], hi[5], hi[6], hi[7], p.mode, p.tie, p.keymask, p.force_keep,
+                                       p.keep_zero_bits, out[6], out[7]);
+    return c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+}
+
+template <int DT, bool LD256>
+__global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t wt = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wt >= p.warp_tiles) return;
+    const int64_t row16 = wt / p.col_blocks;
+    const int64_t cb = wt - row16 * p.col_blocks;
+    const int m0 = lane >> 2, jj = lane & 3;
+    const int64_t col0 = cb * 128 + jj * 32;
+    if (col0 >= p.K) return;  // K % 128 == 64: the upper two lanes of each row are idle
+    const int64_t rA = row16 * 16 + m0, rB = rA + 8;
+
+    uint32_t a_lo[8], a_hi[8], b_lo[8], b_hi[8];
+    const uint16_t* pa = p.A + rA * p.lda + col0;
+    const uint16_t* pb = p.A + rB * p.lda + col0;
+    if (LD256) {
+        ld256(pa, a_lo);
+        ld256(pa + 16, a_hi);
+        ld256(pb, b_lo);
+        ld256(pb + 16, b_hi);
+    } else {
+        ld128x2(pa, a_lo);
+        ld128x2(pa + 16, a_hi);
+        ld128x2(pb, b_lo);
+        ld128x2(pb + 16, b_hi);
+    }
+
+    uint32_t va[8], vb[8];
+    const uint32_t ma = row_span<DT>(a_lo, a_hi, p, va);
+    const uint32_t mb = row_span<DT>(b_lo, b_hi, p, vb);
+
+    const int64_t half_k = p.K >> 1;
+    st256(p.vals + rA * half_k + (col0 >> 1), va);
+    st256(p.vals + rB * half_k + (col0 >> 1), vb);
+
+    // metadata words: row r in the low half, row r+8 in the high half; k1 = which 16-column half
+    const uint32_t w0 = __byte_perm(ma, mb, 0x5410);
+    const uint32_t w1 = __byte_perm(ma, mb, 0x7632);
+    if (p.meta_ref != nullptr) {
+        uint32_t* e = p.meta_ref + row16 * half_k + (cb * 2 + (jj >> 1)) * 32 + m0 * 4 + 2 * (jj & 1);
+        *reinterpret_cast<uint2*>(e) = make_uint2(w0, w1);
+    }
+    if (p.meta_tc != nullptr) {
+        const int64_t tile = row16 >> 3;
+        const int m2 = (int)(row16 & 7);
+        uint32_t* rec = p.meta_tc + ((tile * (p.K >> 7) + cb) * 128 + m0 + 16 * m2) * 4 + jj;
+        rec[0] = w0;       // lane L = m0 + 16*m2      (k1 = 0)
+        rec[32] = w1;      // lane L = m0 + 8 + 16*m2  (k1 = 1)
+    }
+}
+
+// ---------------------------------------------------------------- dense prune (prune_2_4)
+
+template <int DT, bool V128>
+__global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* __restrict__ A, uint16_t* __restrict__ out,
+                                                          int64_t numel, int mode, int tie, uint32_t keymask,
+                                                          uint32_t keep_zero_bits)
+{
+    const int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t base = i8 * 8;
+    if (base >= numel) return;
+    uint32_t in[4] = {0, 0, 0, 0}, o[4];
+    const bool full = base + 8 <= numel;  // otherwise exactly one group of 4 is left
+    if (V128 && full) {
+        uint4 v = *reinterpret_cast<const uint4*>(A + base);
+        in[0] = v.x; in[1] = v.y; in[2] = v.z; in[3] = v.w;
+    } else {
+        uint2 v = *reinterpret_cast<const uint2*>(A + base);
+        in[0] = v.x; in[1] = v.y;
+        if (full) {
+            uint2 w = *reinterpret_cast<const uint2*>(A + base + 4);
+            in[2] = w.x; in[3] = w.y;
+        }
+    }
+    prune_8<DT>(in[0], in[1], in[2], in[3], mode, tie, keymask, keep_zero_bits, o[0], o[1], o[2], o[3]);
+    if (V128 && full) {
+        *reinterpret_cast<uint4*>(out + base) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+        *reinterpret_cast<uint2*>(out + base) = make_uint2(o[0], o[1]);
+        if (full) *reinterpret_cast<uint2*>(out + base + 4) = make_uint2(o[2], o[3]);
+    }
+}
+
+// ---------------------------------------------------------------- metadata layouts
+
+// index, in 16-bit units, of logical word (r, c) in each layout; ncols = K / 16
+__host__ __device__ __forceinline__ int64_t meta_index(int layout, int64_t r, int64_t c, int64_t ncols)
+{
+    if (layout == S24_META_LOGICAL) return r * ncols + c;
+    if (layout == S24_META_REF)  // compress_2_4.py:20-28
+        return (r / 16) * (16 * ncols) + (c / 4) * 64 + (r % 8) * 8 + (c % 4) * 2 + (r / 8) % 2;
+    const int64_t t = r / 128, m2 = (r % 128) / 16, hi = (r / 8) % 2, m0 = r % 8;
+    const int64_t kb = c / 8, j = (c % 8) / 2, k1 = c % 2;
+    const int64_t lane = m0 + 8 * k1 + 16 * m2;
+    return 2 * (((t * (ncols / 8) + kb) * 128 + lane) * 4 + j) + hi;
+}
+
+__global__ void __launch_bounds__(256) meta_convert_kernel(const uint16_t* __restrict__ src, int from,
+                                                           uint16_t* __restrict__ dst, int to, int64_t M,
+                                                           int64_t ncols)
+{
+    // one thread per row pair (r, r+8) and column: both halves of a 32-bit word in REF and TC
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t pairs = (M / 2) * ncols;
+    if (idx >= pairs) return;
+    // enumerate in the order of the REF layout's words so that REF-side accesses coalesce
+    const int64_t words_per_row16 = 8 * ncols;
+    const int64_t row16 = idx / words_per_row16;
+    const int64_t w = idx - row16 * words_per_row16;
+    const int64_t c = (w / 32) * 4 + (w % 4);
+    const int64_t m0 = (w / 4) % 8;
+    const int64_t r = row16 * 16 + m0;
+    const uint16_t lo = src[meta_index(from, r, c, ncols)];
+    const uint16_t hi = src[meta_index(from, r + 8, c, ncols)];
+    if (to == S24_META_LOGICAL) {
+        dst[meta_index(to, r, c, ncols)] = lo;
+        dst[meta_index(to, r + 8, c, ncols)] = hi;
+    } else {
+        *reinterpret_cast<uint32_t*>(dst + meta_index(to, r, c, ncols)) = (uint32_t)lo | ((uint32_t)hi << 16);
+    }
+}
+
+// ---------------------------------------------------------------- host launchers
+
+static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld, int dtype, int mode, int tie,
+                                 void* vals, void* meta_ref, void* meta_tc, cudaStream_t stream)
+{
+    if (A == nullptr || vals == nullptr) return fail(S24_ERR_INVALID_ARG, "prune_compress: null A or vals");
+    if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "prune_compress: bad dtype %d", dtype);
+    if (mode < 0 || mode > 2) return fail(S24_ERR_INVALID_ARG, "prune_compress: bad mode %d", mode);
+    if (tie < 0 || tie > 2) return fail(S24_ERR_INVALID_ARG, "prune_compress: bad tie rule %d", tie);
+    if (M < 0 || K < 0) return fail(S24_ERR_SHAPE, "prune_compress: negative shape");
+    if (M % 32 != 0) return fail(S24_ERR_SHAPE, "Number of rows of dense matrix %lld must be divisible by 32", (long long)M);
+    if (K % 64 != 0) return fail(S24_ERR_SHAPE, "Number of columns of dense matrix %lld must be divisible by 64", (long long)K);
+    if (ld < K || ld % 8 != 0) return fail(S24_ERR_SHAPE, "prune_compress: row stride %lld must be >= K and a multiple of 8", (long long)ld);
+    if (meta_tc != nullptr && (M % 128 != 0 || K % 128 != 0))
+        return fail(S24_ERR_SHAPE, "prune_compress: tensor-core metadata needs M %% 128 == 0 and K %% 128 == 0 (got %lld x %lld)", (long long)M, (long long)K);
+    if (!aligned(A, 16) || !aligned(vals, 32) || !aligned(meta_ref, 16) || !aligned(meta_tc, 16))
+        return fail(S24_ERR_INVALID_ARG, "prune_compress: pointers must be 16-byte aligned (vals 32)");
+    if (M == 0 || K == 0) return S24_OK;
+
+    PcParams p;
+    p.A = static_cast<const uint16_t*>(A);
+    p.lda = ld;
+    p.M = M;
+    p.K = K;
+    p.vals = static_cast<uint16_t*>(vals);
+    p.meta_ref = static_cast<uint32_t*>(meta_ref);
+    p.meta_tc = static_cast<uint32_t*>(meta_tc);
+    p.mode = mode;
+    p.tie = tie;
+    p.keymask = mode == kModeMagnitude ? 0x7FFF7FFFu : 0xFFFFFFFFu;
+    p.force_keep = mode == kModeNone ? 0xFFFFFFFFu : 0u;
+    p.keep_zero_bits = mode == kModeMagnitude ? 0u : 0xFFFFFFFFu;
+    p.col_blocks = (K + 127) / 128;
+    p.warp_tiles = (M / 16) * p.col_blocks;
+    const int64_t blocks = (p.warp_tiles + 7) / 8;
+    if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "prune_compress: matrix too large for one launch");
+    const bool ld256ok = aligned(A, 32) && (ld % 16 == 0);
+    dim3 grid((unsigned)blocks), block(256);
+    if (dtype == S24_FP16) {
+        if (ld256ok) prune_compress_kernel<kFp16, true><<<grid, block, 0, stream>>>(p);
+        else prune_compress_kernel<kFp16, false><<<grid, block, 0, stream>>>(p);
+    } else {
+        if (ld256ok) prune_compress_kernel<kBf16, true><<<grid, block, 0, stream>>>(p);
+        else prune_compress_kernel<kBf16, false><<<grid, block, 0, stream>>>(p);
+    }
+    return check_cuda(cudaGetLastError(), "prune_compress launch");
+}
+
+}  // namespace s24
+
+using namespace s24;
+
+extern "C" int s24_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld, int dtype, int mode, int tie,
+                                  void* vals, void* meta_ref, void* meta_tc, void* stream)
+{
+    if (mode != S24_MODE_SIGNED && mode != S24_MODE_MAGNITUDE)
+        return fail(S24_ERR_INVALID_ARG, "prune_compress: bad mode %d", mode);
+    return launch_prune_compress(A, M, K, ld, dtype, mode, tie, vals, meta_ref, meta_tc, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s24_compress(const void* dense, int64_t M, int64_t K, int64_t ld, int dtype, void* vals,
+                            void* meta_ref, void* meta_tc, void* stream)
+{
+    return launch_prune_compress(dense, M, K, ld, dtype, kModeNone, kTieLower, vals, meta_ref, meta_tc,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s24_prune(const void* A, void* out, int64_t numel, int dtype, int mode, int tie, void* stream)
+{
+    if (A == nullptr || out == nullptr) return fail(S24_ERR_INVALID_ARG, "prune: null pointer");
+    if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "prune: bad dtype %d", dtype);
+    if (mode != S24_MODE_SIGNED && mode != S24_MODE_MAGNITUDE) return fail(S24_ERR_INVALID_ARG, "prune: bad mode %d", mode);
+    if (tie < 0 || tie > 2) return fail(S24_ERR_INVALID_ARG, "prune: bad tie rule %d", tie);
+    if (numel < 0 || numel % 4 != 0)
+        return fail(S24_ERR_SHAPE, "The size of the last dimension must be divisible by 4.");
+    if (!aligned(A, 8) || !aligned(out, 8)) return fail(S24_ERR_INVALID_ARG, "prune: pointers must be 8-byte aligned");
+    if (numel == 0) return S24_OK;
+    const int64_t threads = (numel + 7) / 8;
+    const int64_t blocks = (threads + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "prune: tensor too large for one launch");
+    const uint32_t keymask = mode == kModeMagnitude ? 0x7FFF7FFFu : 0xFFFFFFFFu;
+    const uint32_t kz = mode == kModeMagnitude ? 0u : 0xFFFFFFFFu;
+    const bool v128 = aligned(A, 16) && aligned(out, 16);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint16_t* a = static_cast<const uint16_t*>(A);
+    uint16_t* o = static_cast<uint16_t*>(out);
+    dim3 grid((unsigned)blocks), block(256);
+    if (dtype == S24_FP16) {
+        if (v128) prune_dense_kernel<kFp16, true><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
+        else prune_dense_kernel<kFp16, false><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
+    } else {
+        if (v128) prune_dense_kernel<kBf16, true><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
+        else prune_dense_kernel<kBf16, false><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
+    }
+    return check_cuda(cudaGetLastError(), "prune launch");
+}
+
+extern "C" size_t s24_meta_tc_bytes(int64_t M, int64_t K)
+{
+    if (M <= 0 || K <= 0) return 0;
+    return (size_t)(M * K / 8);
+}
+
+extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int to_layout, int64_t M, int64_t K,
+                                void* stream)
+{
+    if (src == nullptr || dst == nullptr) return fail(S24_ERR_INVALID_ARG, "meta_convert: null pointer");
+    if (from_layout < 0 || from_layout > 2 || to_layout < 0 || to_layout > 2)
+        return fail(S24_ERR_INVALID_ARG, "meta_convert: bad layout");
+    if (M < 0 || K < 0 || M % 32 != 0 || K % 64 != 0)
+        return fail(S24_ERR_SHAPE, "meta_convert: needs M %% 32 == 0 and K %% 64 == 0 (got %lld x %lld)", (long long)M, (long long)K);
+    if ((from_layout == S24_META_TC || to_layout == S24_META_TC) && (M % 128 != 0 || K % 128 != 0))
+        return fail(S24_ERR_SHAPE, "meta_convert: tensor-core layout needs M %% 128 == 0 and K %% 128 == 0 (got %lld x %lld)", (long long)M, (long long)K);
+    if (!aligned(src, 4) || !aligned(dst, 4)) return fail(S24_ERR_INVALID_ARG, "meta_convert: pointers must be 4-byte aligned");
+    if (M == 0 || K == 0) return S24_OK;
+    const int64_t ncols = K / 16;
+    const int64_t pairs = (M / 2) * ncols;
+    const int64_t blocks = (pairs + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "meta_convert: matrix too large for one launch");
+    meta_convert_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(src), from_layout, static_cast<uint16_t*>(dst), to_layout, M, ncols);
+    return check_cuda(cudaGetLastError(), "meta_convert launch");
+}

@@ -1,0 +1,502 @@
+// spmm_tcgen05.cu -- 2:4 structured-sparse GEMM for B200 on tcgen05.mma.sp.
+//
+//   C (M, N) = A24 (M, K) . B (K, N),  16-bit inputs, fp32 accumulation in tensor memory.
+//
+// Replaces the reference's persistent warp-specialised Hopper kernel
+// (compression/gluon_ws_sparse.py:105-278, launcher :560-613; tile walk
+// compression/common.py:150-162) and, with the pruning epilogue, its fused-output variant
+// (compression/kernels/10.1_prune_acc.py:88-154,203-248,359-398).
+//
+// Design (one CTA, or a CTA pair working as one tile engine):
+//   * persistent grid: one CTA (pair) per SM (pair), tiles walked in groups of 8 M-tiles
+//     swept along N so that B tiles stay in L2;
+//   * warp 0: TMA producer.  Per k-block of 128 it loads A values (128 rows x 64 values,
+//     128-byte swizzle), this CTA's part of B (128 rows x BN_CTA columns as 64-column
+//     swizzled atoms) and one 2 KB metadata record into a STAGES-deep shared-memory ring;
+//   * warp 1: MMA issuer (one elected lane).  Per stage: tcgen05.cp moves the metadata
+//     record into 4 TMEM columns, then four tcgen05.mma.sp (K = 32 each) accumulate into
+//     TMEM; tcgen05.commit releases the stage and, after the last k-block, publishes the
+//     accumulator;
+//   * warps 2-5: epilogue.  tcgen05.ld the accumulator (each warp its own 32-lane
+//     quadrant, one row per thread), release TMEM, convert and store;
+//   * CTA pairs (cta_group::2): each CTA loads its own 128 rows of A and half of the B
+//     tile (no multicast), the leader CTA issues 256-row MMAs that read both CTAs' shared
+//     memory, completion is multicast to both CTAs' barriers.
+// Every barrier wait is bounded; on a timeout the kernel records a code in the status word
+// (see s24_device_status), frees its tensor memory and returns.
+#include "s24_common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdlib.h>
+
+namespace s24 {
+
+using namespace ptx;
+
+__device__ int g_status_word = 0;  // first device-side failure since the last s24_device_status()
+
+constexpr int kBlockK = 128;        // logical K per pipeline stage
+constexpr int kRowsPerCta = 128;
+constexpr int kGroupM = 8;          // M-tiles per raster group (compression/common.py:155)
+constexpr int kThreads = 192;       // producer warp, MMA warp, 4 epilogue warps
+constexpr uint32_t kTmemCols = 512;
+
+template <int G, int BN, int STAGES>
+struct GemmCfg {
+    static constexpr int kG = G;
+    static constexpr int kBN = BN;
+    static constexpr int kStages = STAGES;
+    static constexpr int kBNCta = BN / G;                       // B columns loaded per CTA
+    static constexpr int kABytes = kRowsPerCta * 128;           // 128 rows x 64 values x 2 B
+    static constexpr int kBAtomBytes = kBlockK * 128;           // 128 k-rows x 64 columns x 2 B
+    static constexpr int kBBytes = (kBNCta / 64) * kBAtomBytes;
+    static constexpr int kEBytes = 2048;
+    static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;
+    static constexpr int kAccStages = (BN == 256) ? 1 : 2;
+    static constexpr int kECol0 = kAccStages * BN;              // metadata columns follow the accumulators
+    static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(kECol0 + 4 * STAGES <= (int)kTmemCols, "tensor memory budget");
+    static_assert(kBNCta % 64 == 0, "B is loaded in 64-column swizzle atoms");
+};
+
+struct GemmParams {
+    void* C;
+    int64_t ldc;
+    int M, N, K;
+    int bf16;
+    int e_variant;   // bring-up switch for how the metadata column is addressed (0 = default)
+    int* status;
+    // fused output prune (unused by the plain kernel)
+    void* c_vals;
+    uint32_t* c_meta_ref;
+    uint32_t* c_meta_tc;
+};
+
+__device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code)
+{
+    atomicCAS(status, 0, code);
+    *abort_flag = 1;
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm, int& tn)
+{
+    const int group_size = kGroupM * num_n;
+    const int group_id = t / group_size;
+    const int first_m = group_id * kGroupM;
+    const int gm = min(num_m - first_m, kGroupM);
+    const int in_group = t - group_id * group_size;
+    tm = first_m + in_group % gm;
+    tn = in_group / gm;
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int bf16)
+{
+    if (bf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(kThreads, 1)
+spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const __grid_constant__ CUtensorMap tm_e, const GemmParams p)
+{
+    constexpr int G = Cfg::kG;
+    constexpr int BN = Cfg::kBN;
+    constexpr int STAGES = Cfg::kStages;
+    constexpr int ACC = Cfg::kAccStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t smem_a = smem_base;
+    const uint32_t smem_b = smem_a + STAGES * Cfg::kABytes;
+    const uint32_t smem_e = smem_b + STAGES * Cfg::kBBytes;
+    const uint32_t bars = smem_e + STAGES * Cfg::kEBytes;
+    // barrier block: full[STAGES], empty[STAGES], acc_full[ACC], acc_empty[ACC], tmem slot, abort flag
+    const uint32_t bar_full = bars;
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_acc_full = bar_empty + 8 * STAGES;
+    const uint32_t bar_acc_empty = bar_acc_full + 8 * ACC;
+    const uint32_t tmem_slot = bar_acc_empty + 8 * ACC;
+    const uint32_t abort_addr = tmem_slot + 8;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + (abort_addr - smem_base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (G == 2) ? cluster_ctarank() : 0u;
+    const bool leader = cta_rank == 0;
+
+    const int num_m = (p.M + kRowsPerCta * G - 1) / (kRowsPerCta * G);
+    const int num_n = (p.N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_units = (int)gridDim.x / G;
+    const int unit = (int)blockIdx.x / G;
+    const int kblocks = p.K / kBlockK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, G);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < ACC; ++a) {
+            mbar_init(bar_acc_full + 8 * a, 1);
+            mbar_init(bar_acc_empty + 8 * a, 4 * G);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<G>(tmem_slot, kTmemCols);
+        tmem_relinquish<G>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (G == 2) cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            const uint32_t full_owner = (G == 2) ? 0u : cta_rank;  // the leader's barriers collect both CTAs' bytes
+            int s = 0;
+            uint32_t phase = 0;
+            for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
+                int tm, tn;
+                tile_coords(t, num_m, num_n, tm, tn);
+                const int row0 = (tm * G + (int)cta_rank) * kRowsPerCta;
+                const int col0 = tn * BN + (int)cta_rank * Cfg::kBNCta;
+                const int rec0 = (tm * G + (int)cta_rank) * kblocks;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u)) {
+                        report_timeout(p.status, abort_flag, 1);
+                        break;
+                    }
+                    const uint32_t full = (G == 2) ? mapa(bar_full + 8 * s, full_owner) : (bar_full + 8 * s);
+                    mbar_arrive_expect_tx_cluster(full, (uint32_t)Cfg::kStageBytes);
+                    const uint32_t a_dst = smem_a + s * Cfg::kABytes;
+                    const uint32_t b_dst = smem_b + s * Cfg::kBBytes;
+                    const uint32_t e_dst = smem_e + s * Cfg::kEBytes;
+                    if (G == 2) {
+                        tma_load_2d_pair(a_dst, &tm_a, kb * 64, row0, full);
+#pragma unroll
+                        for (int i = 0; i < Cfg::kBNCta / 64; ++i)
+                            tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        tma_load_2d_pair(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
+                    } else {
+                        tma_load_2d(a_dst, &tm_a, kb * 64, row0, full);
+#pragma unroll
+                        for (int i = 0; i < Cfg::kBNCta / 64; ++i)
+                            tma_load_2d(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        tma_load_2d(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
+                    }
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (leader && elect_one()) {
+            const uint32_t idesc = make_idesc_sp_f16(p.bf16, kRowsPerCta * G, BN);
+            int s = 0, a = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
+                if (!mbar_wait(bar_acc_empty + 8 * a, acc_phase ^ 1u)) {
+                    report_timeout(p.status, abort_flag, 3);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(bar_full + 8 * s, phase)) {
+                        report_timeout(p.status, abort_flag, 2);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t e_cols = tmem_base + (uint32_t)(Cfg::kECol0 + 4 * s);
+                    // metadata record: 128 rows of 16 bytes, 8-row core matrices 128 bytes apart
+                    tc_cp_128x128b<G>(e_cols, make_smem_desc(smem_e + s * Cfg::kEBytes, 128, 128, kSwizzleNone));
+                    // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+                    const uint64_t adesc = make_smem_desc(smem_a + s * Cfg::kABytes, 16, 1024, kSwizzle128B);
+                    // B: N-major, 128-byte swizzle; 64-column atoms kBAtomBytes apart (leading),
+                    // 8-k-row groups 1024 bytes apart (stride)
+                    const uint64_t bdesc = make_smem_desc(smem_b + s * Cfg::kBBytes, Cfg::kBAtomBytes, 1024, kSwizzle128B);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // K = 32 per instruction: 32 bytes further along A's rows, 32 k-rows (4096 B) into B,
+                        // metadata column j (even column address + selector bit)
+                        uint32_t sel = (uint32_t)(j & 1), ecol = e_cols + (uint32_t)(j & 2);
+                        if (p.e_variant == 1) { sel = 0; ecol = e_cols + (uint32_t)j; }
+                        else if (p.e_variant == 2) { sel = (uint32_t)j; ecol = e_cols; }
+                        tc_mma_sp_f16<G>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 256),
+                                         idesc | sel, ecol, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    if (G == 2) tc_commit_pair(bar_empty + 8 * s, 3);
+                    else tc_commit<1>(bar_empty + 8 * s);
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                if (G == 2) tc_commit_pair(bar_acc_full + 8 * a, 3);
+                else tc_commit<1>(bar_acc_full + 8 * a);
+                if (++a == ACC) { a = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        int a = 0;
+        uint32_t acc_phase = 0;
+        const uint32_t acc_empty_leader = (G == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
+        for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
+            int tm, tn;
+            tile_coords(t, num_m, num_n, tm, tn);
+            if (!mbar_wait(bar_acc_full + 8 * a, acc_phase)) {
+                if (lane == 0) report_timeout(p.status, abort_flag, 4);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
+            uint32_t packed[BN / 2];
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    packed[c * 16 + i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), p.bf16);
+            }
+            // accumulator is in registers: hand the TMEM stage back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+            if (++a == ACC) { a = 0; acc_phase ^= 1u; }
+
+            const int64_t row = (int64_t)(tm * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
+            const int col0 = tn * BN;
+            if (row < p.M) {
+                uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
+#pragma unroll
+                for (int c8 = 0; c8 < BN / 8; ++c8) {
+                    if (col0 + c8 * 8 < p.N)
+                        *reinterpret_cast<uint4*>(crow + c8 * 8) =
+                            make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (G == 2) cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<G>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+static int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t inner,
+                       uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                       CUtensorMapSwizzle swz, const char* what)
+{
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return fail(S24_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(S24_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+    return S24_OK;
+}
+
+struct GemmArgs {
+    const void* vals;
+    const void* meta_tc;
+    const void* B;
+    int64_t M, N, K, ldb;
+    int dtype;
+    GemmParams p;
+};
+
+template <class Cfg>
+static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
+{
+    CUtensorMap tm_a, tm_b, tm_e;
+    const CUtensorMapDataType dt = g.dtype == S24_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    int rc = make_map_2d(&tm_a, dt, 2, g.vals, (uint64_t)(g.K / 2), (uint64_t)g.M, (uint64_t)g.K, 64, kRowsPerCta,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "A values");
+    if (rc) return rc;
+    rc = make_map_2d(&tm_b, dt, 2, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, kBlockK,
+                     CU_TENSOR_MAP_SWIZZLE_128B, "B");
+    if (rc) return rc;
+    const uint64_t records = (uint64_t)(g.M / 128) * (uint64_t)(g.K / 128);
+    rc = make_map_2d(&tm_e, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, g.meta_tc, 128, records * 4, 512, 128, 4,
+                     CU_TENSOR_MAP_SWIZZLE_NONE, "metadata");
+    if (rc) return rc;
+
+    rc = check_cuda(cudaFuncSetAttribute(spmm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                    "cudaFuncSetAttribute(max dynamic shared memory)");
+    if (rc) return rc;
+    const int num_m = (int)((g.M + kRowsPerCta * Cfg::kG - 1) / (kRowsPerCta * Cfg::kG));
+    const int num_n = (int)((g.N + Cfg::kBN - 1) / Cfg::kBN);
+    const int tiles = num_m * num_n;
+    int units = sm_count() / Cfg::kG;
+    if (units > tiles) units = tiles;
+    if (units < 1) units = 1;
+
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(units * Cfg::kG));
+    lc.blockDim = dim3(kThreads);
+    lc.dynamicSmemBytes = Cfg::kSmemBytes;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = Cfg::kG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&lc, spmm_kernel<Cfg>, tm_a, tm_b, tm_e, g.p), "sparse GEMM launch");
+}
+
+static int* status_word_address()
+{
+    // device address of g_status_word for the current device (looked up once per device)
+    static int* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_status_word) != cudaSuccess) return nullptr;
+        cached[dev] = static_cast<int*>(ptr);
+    }
+    return cached[dev];
+}
+
+static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                    int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, cudaStream_t stream)
+{
+    if (vals == nullptr || meta_tc == nullptr || B == nullptr || C == nullptr)
+        return fail(S24_ERR_INVALID_ARG, "spmm: null pointer");
+    if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "spmm: bad dtype %d", dtype);
+    if (M <= 0 || N <= 0 || K <= 0 || M % 128 != 0 || K % 128 != 0 || N % 8 != 0)
+        return fail(S24_ERR_SHAPE, "spmm: needs M %% 128 == 0, K %% 128 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)",
+                    (long long)M, (long long)N, (long long)K);
+    if (M > 0x7FFFFF00ll || N > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return fail(S24_ERR_SHAPE, "spmm: dimension too large");
+    if (ldb < N || ldb % 8 != 0 || ldc < N || ldc % 8 != 0)
+        return fail(S24_ERR_SHAPE, "spmm: ldb/ldc must be >= N and multiples of 8 (got %lld, %lld)", (long long)ldb, (long long)ldc);
+    if (!aligned(vals, 16) || !aligned(meta_tc, 16) || !aligned(B, 16) || !aligned(C, 16))
+        return fail(S24_ERR_INVALID_ARG, "spmm: pointers must be 16-byte aligned");
+    int* status = status_word_address();
+    if (status == nullptr) return fail(S24_ERR_CUDA, "spmm: cannot resolve the device status word");
+
+    GemmArgs g;
+    g.vals = vals;
+    g.meta_tc = meta_tc;
+    g.B = B;
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.ldb = ldb;
+    g.dtype = dtype;
+    g.p.C = C;
+    g.p.ldc = ldc;
+    g.p.M = (int)M;
+    g.p.N = (int)N;
+    g.p.K = (int)K;
+    g.p.bf16 = dtype == S24_BF16;
+    {
+        const char* v = getenv("S24_E_VARIANT");
+        g.p.e_variant = v ? atoi(v) : 0;
+    }
+    g.p.status = status;
+    g.p.c_vals = nullptr;
+    g.p.c_meta_ref = nullptr;
+    g.p.c_meta_tc = nullptr;
+
+    int bm = cfg ? cfg->bm : 0, bn = cfg ? cfg->bn : 0;
+    if (bm == 0) bm = (M % 256 == 0 || M > 1024) ? 256 : 128;
+    if (bn == 0) bn = (bm == 256 && N >= 256) ? 256 : 128;
+    if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4>>(g, stream);
+    if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6>>(g, stream);
+    if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 6>>(g, stream);
+    return fail(S24_ERR_UNSUPPORTED, "spmm: no kernel for tile %d x %d (have 256x256, 256x128, 128x128)", bm, bn);
+}
+
+}  // namespace s24
+
+using namespace s24;
+
+extern "C" int s24_spmm(const void* vals, const void* meta_tc, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                        int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, void* stream)
+{
+    return run_spmm(vals, meta_tc, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const void* B, void* C, int64_t M, int64_t N,
+                                 int64_t K, int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg,
+                                 void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (workspace == nullptr || workspace_bytes < s24_meta_tc_bytes(M, K))
+        return fail(S24_ERR_INVALID_ARG, "spmm_ref_meta: workspace of %zu bytes needed, %zu given", s24_meta_tc_bytes(M, K),
+                    workspace_bytes);
+    if (!aligned(workspace, 16)) return fail(S24_ERR_INVALID_ARG, "spmm_ref_meta: workspace must be 16-byte aligned");
+    int rc = s24_meta_convert(meta_ref, S24_META_REF, workspace, S24_META_TC, M, K, stream);
+    if (rc) return rc;
+    return run_spmm(vals, workspace, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s24_spmm_prune_out(const void*, const void*, const void*, void*, void*, void*, int64_t, int64_t, int64_t,
+                                  int64_t, int, const s24_tile_cfg*, void*)
+{
+    return fail(S24_ERR_UNSUPPORTED, "spmm_prune_out: not built yet");
+}
+
+extern "C" int s24_device_status(void* stream)
+{
+    int* status = status_word_address();
+    if (status == nullptr) return fail(S24_ERR_CUDA, "device_status: cannot resolve the device status word");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    int rc = check_cuda(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, s), "device_status copy");
+    if (rc) return rc;
+    rc = check_cuda(cudaStreamSynchronize(s), "device_status sync");
+    if (rc) return rc;
+    if (host == 0) return S24_OK;
+    cudaMemsetAsync(status, 0, sizeof(int), s);
+    cudaStreamSynchronize(s);
+    return fail(S24_ERR_TIMEOUT, "a device-side wait timed out (code %d: 1 producer/empty, 2 mma/full, 3 mma/accumulator, 4 epilogue)", host);
+}

@@ -1,0 +1,213 @@
+"""torch-tensor front end of the C ABI.
+
+Each function validates its tensors the way the reference's functions do (same
+exception types for the same conditions), allocates outputs with torch on the input's
+device (so the caller's allocator and CUDA-graph capture work as with the reference,
+gluon_ws_sparse.py:563), and enqueues the library call on torch's current stream.
+There is no fallback: CPU tensors or a missing libs24.so raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+_DT = {torch.float16: L.FP16, torch.bfloat16: L.BF16}
+_MODE = {"signed": L.MODE_SIGNED, "magnitude": L.MODE_MAGNITUDE}
+_TIE = {"reference": L.TIE_REFERENCE, "torch": L.TIE_REFERENCE, "lower": L.TIE_LOWER, "higher": L.TIE_HIGHER}
+
+
+def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("s24 kernels run on CUDA tensors only (there is no CPU path)")
+    dev = {t.device for t in ts if t is not None}
+    if len(dev) > 1:
+        raise RuntimeError(f"tensors live on different devices: {sorted(map(str, dev))}")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype not in _DT:
+        raise RuntimeError(f"Invalid datatype {t.dtype} of dense matrix")
+    return _DT[t.dtype]
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def meta_tc_numel(M: int, K: int) -> int:
+    """int32 elements of a tensor-core-layout metadata buffer for an (M, K) matrix."""
+    return int(L.lib().s24_meta_tc_bytes(M, K)) // 4
+
+
+def prune(t: torch.Tensor, mode: str = "signed", tie: str = "reference") -> torch.Tensor:
+    """2:4 prune along the last dimension; new tensor (compression/prune.py:57-96)."""
+    if t.size(-1) % 4 != 0:
+        raise ValueError("The size of the last dimension must be divisible by 4.")
+    _require_cuda(t)
+    dt = _dtype_code(t)
+    src = t.contiguous()
+    out = torch.empty_like(src)
+    with torch.cuda.device(t.device):
+        L.check(L.lib().s24_prune(_p(src), _p(out), src.numel(), dt, _MODE[mode], _TIE[tie], _stream(t)))
+    return out.view(t.shape)
+
+
+def _check_compress_shape(dense: torch.Tensor) -> Tuple[int, int]:
+    # same conditions and exception types as compress_2_4.py:33-65 and :10
+    if dense.dim() != 2:
+        raise RuntimeError(f"Expected 2-dimensional dense tensor, got {dense.dim()}-dimensional tensor")
+    _dtype_code(dense)
+    m, k = dense.shape
+    if m % 32 != 0:
+        raise RuntimeError(f"Number of rows of dense matrix {m} must be divisible by 32")
+    if k % 16 != 0:
+        raise RuntimeError(f"Number of columns of dense matrix {k} must be divisible by 16")
+    assert (k // 16) % 4 == 0, f"The number of metadata cols must be at least 4, current number: {k // 16}"
+    return m, k
+
+
+def _row_major(t: torch.Tensor) -> torch.Tensor:
+    if t.stride(-1) != 1 or t.stride(0) % 8 != 0 or t.stride(0) < t.shape[1] or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def compress(dense: torch.Tensor, want_ref: bool = True, want_tc: bool = False):
+    """compress_dense_to_sparse from non-zero flags (compression/compress_2_4.py:32-161).
+
+    Returns (values (M, K/2), E (M/16, K) int16 or None, meta_tc int32 or None).
+    """
+    m, k = _check_compress_shape(dense)
+    _require_cuda(dense)
+    d = _row_major(dense)
+    vals = torch.empty((m, k // 2), dtype=dense.dtype, device=dense.device)
+    e = torch.empty((m // 16, k), dtype=torch.int16, device=dense.device) if want_ref else None
+    tc = torch.empty((meta_tc_numel(m, k),), dtype=torch.int32, device=dense.device) if want_tc else None
+    if m * k:
+        with torch.cuda.device(dense.device):
+            L.check(L.lib().s24_compress(_p(d), m, k, d.stride(0), _DT[dense.dtype], _p(vals), _p(e), _p(tc),
+                                         _stream(dense)))
+    return vals, e, tc
+
+
+def prune_compress(A: torch.Tensor, mode: str = "signed", tie: str = "reference", want_ref: bool = True,
+                   want_tc: bool = False):
+    """Fused prune + compress, one pass over A (kernels/11.1_2_kernel_baseline.py:171-203,256-279).
+
+    Returns (values (M, K/2), E (M/16, K) int16 or None, meta_tc int32 or None).
+    """
+    m, k = _check_compress_shape(A)
+    _require_cuda(A)
+    a = _row_major(A)
+    vals = torch.empty((m, k // 2), dtype=A.dtype, device=A.device)
+    e = torch.empty((m // 16, k), dtype=torch.int16, device=A.device) if want_ref else None
+    tc = torch.empty((meta_tc_numel(m, k),), dtype=torch.int32, device=A.device) if want_tc else None
+    if m * k:
+        with torch.cuda.device(A.device):
+            L.check(L.lib().s24_prune_compress(_p(a), m, k, a.stride(0), _DT[A.dtype], _MODE[mode], _TIE[tie],
+                                               _p(vals), _p(e), _p(tc), _stream(A)))
+    return vals, e, tc
+
+
+_LAYOUT = {"logical": L.META_LOGICAL, "ref": L.META_REF, "tc": L.META_TC}
+
+
+def meta_convert(src: torch.Tensor, from_layout: str, to_layout: str, M: int, K: int) -> torch.Tensor:
+    """Re-lay metadata of an (M, K) matrix between "logical", "ref" and "tc"."""
+    _require_cuda(src)
+    src = src.contiguous()
+    if to_layout == "tc":
+        dst = torch.empty((meta_tc_numel(M, K),), dtype=torch.int32, device=src.device)
+    elif to_layout == "ref":
+        dst = torch.empty((M // 16, K), dtype=torch.int16, device=src.device)
+    else:
+        dst = torch.empty((M, K // 16), dtype=torch.int16, device=src.device)
+    with torch.cuda.device(src.device):
+        L.check(L.lib().s24_meta_convert(_p(src), _LAYOUT[from_layout], _p(dst), _LAYOUT[to_layout], M, K,
+                                         _stream(src)))
+    return dst
+
+
+def _tile_cfg(manual_config: Optional[dict]):
+    if not manual_config:
+        return None
+    cfg = L.TileCfg(int(manual_config.get("BM", 0)), int(manual_config.get("BN", 0)),
+                    int(manual_config.get("buffers", 0)), 0)
+    return ctypes.byref(cfg)
+
+
+def _check_gemm(vals: torch.Tensor, B: torch.Tensor) -> Tuple[int, int, int]:
+    if vals.dim() != 2 or B.dim() != 2:
+        raise RuntimeError("sparse matmul expects 2-dimensional operands")
+    M, K2 = vals.shape
+    K, N = B.shape
+    if 2 * K2 != K:
+        raise RuntimeError(f"compressed A has {K2} columns but B has {K} rows (expected K/2 = {K // 2})")
+    if vals.dtype != B.dtype:
+        raise RuntimeError(f"operand dtypes differ: {vals.dtype} vs {B.dtype}")
+    _dtype_code(vals)
+    if M % 128 != 0 or K % 128 != 0 or N % 8 != 0:
+        raise RuntimeError(f"sparse matmul needs M % 128 == 0, K % 128 == 0, N % 8 == 0 (got M={M}, N={N}, K={K})")
+    return M, N, K
+
+
+def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: str = "tc",
+         manual_config: Optional[dict] = None, out: Optional[torch.Tensor] = None,
+         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A24 @ B with fp32 accumulation (compression/gluon_ws_sparse.py:560-613).
+
+    meta_layout "tc": `meta` is the tensor-core layout.  "ref": `meta` is the reference's
+    E (M/16, K) int16; it is re-laid into `workspace` (allocated here if not given) first.
+    """
+    _require_cuda(vals, meta, B)
+    M, N, K = _check_gemm(vals, B)
+    v = vals.contiguous()
+    b = _row_major(B)
+    c = out if out is not None else torch.empty((M, N), dtype=vals.dtype, device=vals.device)
+    cfg = _tile_cfg(manual_config)
+    with torch.cuda.device(vals.device):
+        if meta_layout == "tc":
+            L.check(L.lib().s24_spmm(_p(v), _p(meta), _p(b), _p(c), M, N, K, b.stride(0), c.stride(0),
+                                     _DT[vals.dtype], cfg, _stream(vals)))
+        elif meta_layout == "ref":
+            if meta.numel() != M * K // 16:
+                raise RuntimeError(f"E has {meta.numel()} elements, expected {M * K // 16} for ({M}, {K})")
+            if workspace is None:
+                workspace = torch.empty((meta_tc_numel(M, K),), dtype=torch.int32, device=vals.device)
+            L.check(L.lib().s24_spmm_ref_meta(_p(v), _p(meta.contiguous()), _p(b), _p(c), M, N, K, b.stride(0),
+                                              c.stride(0), _DT[vals.dtype], cfg, _p(workspace),
+                                              workspace.numel() * 4, _stream(vals)))
+        else:
+            raise ValueError(f"unknown metadata layout {meta_layout!r}")
+    return c
+
+
+def spmm_prune_out(vals: torch.Tensor, meta_tc: torch.Tensor, B: torch.Tensor, want_ref: bool = True,
+                   want_tc: bool = False, manual_config: Optional[dict] = None):
+    """Sparse GEMM whose epilogue 2:4-prunes and compresses the accumulator along N
+    (compression/kernels/10.1_prune_acc.py:88-154,624-678).
+
+    Returns (C_vals (M, N/2), C_meta (M/16, N) int16 or None, C_meta_tc or None).
+    """
+    _require_cuda(vals, meta_tc, B)
+    M, N, K = _check_gemm(vals, B)
+    if N % 128 != 0:
+        raise RuntimeError(f"fused output prune needs N % 128 == 0 (got {N})")
+    v = vals.contiguous()
+    b = _row_major(B)
+    cv = torch.empty((M, N // 2), dtype=vals.dtype, device=vals.device)
+    ce = torch.empty((M // 16, N), dtype=torch.int16, device=vals.device) if want_ref else None
+    ct = torch.empty((meta_tc_numel(M, N),), dtype=torch.int32, device=vals.device) if want_tc else None
+    with torch.cuda.device(vals.device):
+        L.check(L.lib().s24_spmm_prune_out(_p(v), _p(meta_tc), _p(b), _p(cv), _p(ce), _p(ct), M, N, K,
+                                           b.stride(0), _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
+    return cv, ce, ct

@@ -1,0 +1,181 @@
+/*
+ * s24.h -- C ABI of the B200 (sm_100a) 2:4 structured-sparsity library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as
+ * void*, i.e. a cudaStream_t / CUstream; NULL = the legacy default stream).  Nothing
+ * here allocates device memory, synchronises the device or throws: each call enqueues
+ * work on the given stream and returns S24_OK or a negative S24_ERR_* code whose text is
+ * available (per calling thread) from s24_last_error().
+ *
+ * The entry points replace, one for one, the GPU work behind these functions of the
+ * reference project (paths relative to its root):
+ *
+ *   s24_prune            compression/prune.py:57-96           prune_2_4
+ *   s24_compress         compression/compress_2_4.py:32-161   compress_dense_to_sparse
+ *   s24_prune_compress   compression/kernels/11.1_2_kernel_baseline.py:171-203,256-279
+ *                                                             ws_tma_compress_2_4_kernel
+ *   s24_meta_convert     compression/compress_2_4.py:6-30     _calculate_meta_reordering_offsets
+ *   s24_spmm             compression/gluon_ws_sparse.py:244-278,560-613  run_sparse_ws_matmul
+ *   s24_spmm_ref_meta    same launcher, fed the reference's metadata layout directly
+ *   s24_spmm_prune_out   compression/kernels/10.1_prune_acc.py:88-154,359-398,624-678
+ *
+ * Element types: S24_FP16 / S24_BF16, 16-bit storage, row-major matrices.
+ *
+ * Metadata layouts (all describe the same logical array meta[M][K/16] of 16-bit words,
+ * group 4c+j of a row in bits 4j..4j+3 of word c, each group coded idx0 | idx1 << 2):
+ *   S24_META_LOGICAL  meta[r][c], int16 (M, K/16)
+ *   S24_META_REF      the reference's reordered buffer viewed (M/16, K) int16:
+ *                     E[r/16][(c/4)*64 + (r%8)*8 + (c%4)*2 + (r/8)%2] = meta[r][c]
+ *   S24_META_TC       records of 2048 bytes per (128-row tile t, 128-column block kb),
+ *                     ordered [t][kb]; a record is 128 lanes x 4 words, lane
+ *                     L = m0 + 8*k1 + 16*m2 and word j holding
+ *                     meta[128t+16*m2+m0][8kb+2j+k1] | meta[128t+16*m2+8+m0][8kb+2j+k1] << 16.
+ *                     This is the image tcgen05.cp (128x128b) moves into tensor memory for
+ *                     four consecutive tcgen05.mma.sp instructions of K = 32.
+ */
+#ifndef S24_H_
+#define S24_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define S24_API __attribute__((visibility("default")))
+#else
+#define S24_API
+#endif
+
+#define S24_VERSION 1
+
+/* status codes */
+#define S24_OK 0
+#define S24_ERR_INVALID_ARG (-1)   /* null pointer, bad enum, bad alignment */
+#define S24_ERR_SHAPE (-2)         /* a divisibility or range rule on M, N, K, ld* failed */
+#define S24_ERR_CUDA (-3)          /* a CUDA runtime / driver call failed */
+#define S24_ERR_UNSUPPORTED (-4)   /* valid request this build has no kernel for */
+#define S24_ERR_TIMEOUT (-5)       /* a bounded device-side wait gave up (status word set) */
+
+/* element types */
+#define S24_FP16 0
+#define S24_BF16 1
+
+/* which keys rank the four elements of a group */
+#define S24_MODE_SIGNED 0          /* the values themselves: prune.py:85 (reference default) */
+#define S24_MODE_MAGNITUDE 1       /* |value| */
+
+/* which element survives when the 2nd and 3rd largest keys are equal */
+#define S24_TIE_REFERENCE 0        /* exactly what the reference's CPU torch.topk does */
+#define S24_TIE_LOWER 1            /* lower index survives (kernels/10.1_prune_acc.py:100-105) */
+#define S24_TIE_HIGHER 2           /* higher index survives (kernels/11.1_2_kernel_baseline.py:95-100) */
+
+/* metadata layouts */
+#define S24_META_LOGICAL 0
+#define S24_META_REF 1
+#define S24_META_TC 2
+
+/* Optional tile choice for the GEMM entry points; NULL or zeros = heuristic.
+ * Mirrors the keys of the reference's manual_config (gluon_ws_sparse.py:629-636). */
+typedef struct s24_tile_cfg {
+    int bm;        /* rows per tile: 128 (one CTA) or 256 (CTA pair), 0 = auto */
+    int bn;        /* columns per tile: 128 or 256, 0 = auto */
+    int stages;    /* depth of the shared-memory ring, 0 = auto */
+    int reserved;
+} s24_tile_cfg;
+
+S24_API int s24_version(void);
+
+/* text of the last error on the calling thread ("" if none) */
+S24_API const char* s24_last_error(void);
+
+/*
+ * prune_2_4 (compression/prune.py:57-96): for every contiguous group of four along the
+ * last dimension zero the two smallest keys; survivors keep their bit patterns, dropped
+ * elements become +0.0.  `numel` elements are read from A and written to out as one flat,
+ * contiguous array (any leading shape); numel % 4 must be 0 (the reference's
+ * ValueError, prune.py:76-77) and both pointers 8-byte aligned.  out may equal A.
+ */
+S24_API int s24_prune(const void* A, void* out, int64_t numel, int dtype, int mode, int tie, void* stream);
+
+/*
+ * compress_dense_to_sparse (compression/compress_2_4.py:32-161) for 16-bit types: from
+ * the non-zero flags of `dense` (M, K; row stride ld elements) write the two stored
+ * values of each group to vals (M, K/2 contiguous) and the metadata in the reference's
+ * reordered layout to meta_ref ((M/16, K) int16) and/or in the tensor-core layout to
+ * meta_tc (s24_meta_tc_bytes(M, K) bytes); either metadata pointer may be NULL.
+ * Needs M % 32 == 0, K % 64 == 0 (compress_2_4.py:10,57-65), ld % 8 == 0, 16-byte aligned
+ * pointers; meta_tc additionally needs M % 128 == 0 and K % 128 == 0.
+ */
+S24_API int s24_compress(const void* dense, int64_t M, int64_t K, int64_t ld, int dtype,
+                 void* vals, void* meta_ref, void* meta_tc, void* stream);
+
+/*
+ * Fused prune + compress in one pass over A (the reference's standalone kernel,
+ * compression/kernels/11.1_2_kernel_baseline.py:171-203): identical results to
+ * s24_prune followed by s24_compress, A read once, nothing else read.
+ * Algorithmic traffic 3.125 bytes per element of A with one metadata layout.
+ */
+S24_API int s24_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld, int dtype, int mode, int tie,
+                       void* vals, void* meta_ref, void* meta_tc, void* stream);
+
+/* bytes of a S24_META_TC buffer for an (M, K) matrix: M * K / 8 (one bit per element) */
+S24_API size_t s24_meta_tc_bytes(int64_t M, int64_t K);
+
+/*
+ * Convert metadata between layouts (compression/compress_2_4.py:6-30 gives
+ * LOGICAL -> REF).  M % 32 == 0 and K % 64 == 0; any side in S24_META_TC needs
+ * M % 128 == 0 and K % 128 == 0.  src and dst must not overlap.
+ */
+S24_API int s24_meta_convert(const void* src, int from_layout, void* dst, int to_layout,
+                     int64_t M, int64_t K, void* stream);
+
+/*
+ * run_sparse_ws_matmul (compression/gluon_ws_sparse.py:560-613):
+ *   C (M, N) = A24 (M, K) . B (K, N), fp32 accumulation, C in the element type of A/B.
+ * A24 is given as vals (M, K/2 contiguous) + meta_tc (S24_META_TC).  B has row stride
+ * ldb, C row stride ldc (elements).  M % 128 == 0, K % 128 == 0, N % 8 == 0,
+ * ldb % 8 == 0, ldc % 8 == 0, 16-byte aligned pointers.
+ */
+S24_API int s24_spmm(const void* vals, const void* meta_tc, const void* B, void* C,
+             int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,
+             const s24_tile_cfg* cfg, void* stream);
+
+/*
+ * Same product with the metadata in the reference's layout (the E a caller of
+ * run_sparse_ws_matmul holds, gluon_ws_sparse.py:655-658).  The layout conversion runs
+ * first on the same stream into `workspace`, which the caller provides:
+ * workspace_bytes >= s24_meta_tc_bytes(M, K), 16-byte aligned.
+ */
+S24_API int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const void* B, void* C,
+                      int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,
+                      const s24_tile_cfg* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Sparse GEMM whose epilogue 2:4-prunes the fp32 accumulator along N and stores it
+ * compressed (compression/kernels/10.1_prune_acc.py:88-154,624-678): C_vals (M, N/2) in
+ * the element type (rounded after selection, :241) and metadata of the (M, N) result in
+ * the reference layout C_meta_ref ((M/16, N) int16) and/or C_meta_tc; either may be NULL.
+ * Keys are the signed accumulator values and ties keep the lower index, as in
+ * 10.1_prune_acc.py:100-105.  Needs N % 128 == 0 in addition to the s24_spmm rules.
+ */
+S24_API int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void* B,
+                       void* C_vals, void* C_meta_ref, void* C_meta_tc,
+                       int64_t M, int64_t N, int64_t K, int64_t ldb, int dtype,
+                       const s24_tile_cfg* cfg, void* stream);
+
+/*
+ * Debug / test aid (no counterpart in the reference): every device-side wait in the GEMM
+ * kernels is bounded; if one gives up the kernel records a code and returns.  This call
+ * synchronises `stream`, returns S24_OK if no kernel on the current device has reported a
+ * failure since the last call, else S24_ERR_TIMEOUT (code in s24_last_error()), and clears
+ * the record.
+ */
+S24_API int s24_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* S24_H_ */

@@ -10,11 +10,12 @@ unmodified, runs them on CPU on seeded inputs and stores inputs + outputs as raw
 patterns.  It also measures how the reference's ``torch.topk`` breaks ties and writes
 that as a 729-entry weak-ordering table to
 
-    tests/golden/tie_table.json                       (the fixture)
-    oracle/tie_table.inc                              (read by the CPU oracle)
-    gpu-compression-kernel_b200/csrc/tie_table.inc    (compiled into the CUDA library)
+    tests/golden/tie_table.json     (the fixture)
+    oracle/tie_table.inc            (read by the CPU oracle)
 
-tests/test_oracle_golden.py checks that the three copies agree.
+tests/test_oracle_golden.py checks that the two copies agree; the CUDA library states the
+same behaviour as a rule (csrc/prune_core.cuh, keep_mask_scalar) which
+tests/test_prune_core_host.py checks against the table for all 75 weak orderings.
 """
 import itertools
 import json
@@ -89,7 +90,6 @@ def main():
     table = measure_tie_table()
     inc = ",\n".join(", ".join(str(int(v)) for v in table[i:i + 27]) for i in range(0, 729, 27)) + "\n"
     (ROOT / "oracle" / "tie_table.inc").write_text(inc)
-    (ROOT / "gpu-compression-kernel_b200" / "csrc" / "tie_table.inc").write_text(inc)
     (HERE / "tie_table.json").write_text(json.dumps({
         "source": "compression/prune.py:85 torch.topk(k=2, largest=False) on CPU, torch " + torch.__version__,
         "index": "sum over pairs (01,02,03,12,13,23) of t*3^p, t=0 if k_i<k_j, 1 if equal, 2 if greater",

@@ -1,0 +1,71 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/s24.h declares."""
+import ctypes
+import re
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+PKG = ROOT / "gpu-compression-kernel_b200"
+sys.path.insert(0, str(PKG))
+
+
+@pytest.fixture(scope="module")
+def built():
+    sys.path.insert(0, str(PKG))
+    import build as s24_build
+    return s24_build.build()
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "s24.h").read_text()
+    return sorted(set(re.findall(r"S24_API[^;(]*?\b(s24_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for want in ("s24_version", "s24_last_error", "s24_prune", "s24_compress", "s24_prune_compress",
+                 "s24_meta_tc_bytes", "s24_meta_convert", "s24_spmm", "s24_spmm_ref_meta", "s24_spmm_prune_out",
+                 "s24_device_status"):
+        assert want in names
+
+
+def test_library_exports_every_declared_symbol(built):
+    lib = ctypes.CDLL(str(built))
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in include/s24.h but not exported"
+
+
+def test_ctypes_signatures_cover_the_header(built):
+    from s24 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+    L = _lib.lib()
+    assert L.s24_version() == 1
+    assert L.s24_meta_tc_bytes(256, 512) == 256 * 512 // 8
+
+
+def test_argument_errors_need_no_gpu(built):
+    # validation happens before any CUDA call, so it can be exercised on a CPU-only box
+    from s24 import _lib
+    L = _lib.lib()
+    assert L.s24_prune(None, None, 8, 0, 0, 0, None) == _lib.ERR_INVALID_ARG
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert L.s24_prune(p, p, 6, 0, 0, 0, None) == _lib.ERR_SHAPE
+    assert "divisible by 4" in _lib.last_error()
+    assert L.s24_prune_compress(p, 48, 64, 64, 0, 0, 0, p, p, None, None) == _lib.ERR_SHAPE
+    assert "divisible by 32" in _lib.last_error()
+    assert L.s24_prune_compress(p, 32, 80, 80, 0, 0, 0, p, p, None, None) == _lib.ERR_SHAPE
+    assert L.s24_prune_compress(p, 32, 64, 64, 7, 0, 0, p, p, None, None) == _lib.ERR_INVALID_ARG
+    assert L.s24_spmm(p, p, p, p, 100, 128, 128, 128, 128, 0, None, None) == _lib.ERR_SHAPE
+    assert L.s24_meta_convert(p, 1, p, 2, 64, 128, None) == _lib.ERR_SHAPE
+
+
+def test_cpu_tensors_are_rejected_loudly(built):
+    import torch
+    import s24
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        s24.prune(torch.zeros(4, 8, dtype=torch.float16))
+    with pytest.raises(ValueError):
+        s24.prune(torch.zeros(4, 6, dtype=torch.float16))

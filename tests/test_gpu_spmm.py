@@ -1,0 +1,152 @@
+"""GPU parity of the tcgen05 sparse GEMM: C = prune_2_4(A) @ B against an fp32-accumulated
+reference (compression/gluon_ws_sparse.py:660), rtol = atol = 1e-2, through the drop-in
+launchers and the C ABI.  Small cases use the CPU oracle's GEMM; larger ones an fp32
+torch matmul (TF32 off) of the oracle-pruned A."""
+import numpy as np
+import pytest
+import torch
+
+from util import ODT, bits, from_bits, load_dropin, oracle, randn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+RTOL = ATOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def mods():
+    import s24
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return {"s24": s24, "ws": load_dropin("gluon_ws_sparse.py"), "two": load_dropin("kernels/11.1_2_kernel_baseline.py")}
+
+
+def _status_ok(s24):
+    from s24 import _lib
+    rc = _lib.lib().s24_device_status(None)
+    assert rc == 0, _lib.last_error()
+
+
+def _prepare(M, K, N, dtype, seed, scale=1.0):
+    A = randn((M, K), dtype, seed, scale)
+    B = randn((K, N), dtype, seed + 1)
+    ap = oracle.prune(bits(A), ODT[dtype])
+    vals, ml, e = oracle.compress(ap, ODT[dtype])
+    return A, B, ap, vals, ml, e
+
+
+def _reference(ap_bits, B, dtype):
+    Ap = from_bits(ap_bits, dtype, DEV).float()
+    return Ap @ B.to(DEV).float()
+
+
+def _check(C, ref32):
+    torch.testing.assert_close(C.float(), ref32.to(C.dtype).float(), rtol=RTOL, atol=ATOL)
+    # and against the unrounded sums with a little room for the output rounding
+    torch.testing.assert_close(C.float(), ref32, rtol=RTOL, atol=ATOL + 4e-3 * float(ref32.abs().max()))
+
+
+@pytest.mark.parametrize("cfg", [{"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}])
+def test_identity_b_reveals_decompressed_a(mods, cfg):
+    """B = I makes C the dense 2:4 matrix itself, exactly: checks values, metadata layout
+    and operand descriptors independently of any accumulation."""
+    s24 = mods["s24"]
+    M, K = 256, 256
+    A, _, ap, vals, ml, e = _prepare(M, K, K, torch.float16, 11)
+    B = torch.eye(K, dtype=torch.float16)
+    tc = torch.from_numpy(oracle.meta_tc(ml, K).view(np.int32)).to(DEV)
+    C = s24.spmm(from_bits(vals, torch.float16, DEV), tc, B.to(DEV), manual_config=cfg)
+    _status_ok(s24)
+    assert torch.equal(C.float().cpu(), from_bits(ap, torch.float16).float())   # -0.0 == +0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 256, 512), (384, 200, 384), (512, 1032, 1280), (1024, 768, 2048)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}])
+def test_spmm_vs_fp32_reference(mods, M, N, K, dtype, cfg):
+    s24 = mods["s24"]
+    A, B, ap, vals, ml, e = _prepare(M, K, N, dtype, 100 + M + N + K)
+    tc = torch.from_numpy(oracle.meta_tc(ml, K).view(np.int32)).to(DEV)
+    C = s24.spmm(from_bits(vals, dtype, DEV), tc, B.to(DEV), manual_config=cfg)
+    _status_ok(s24)
+    assert C.shape == (M, N) and C.dtype == dtype
+    _check(C, _reference(ap, B, dtype))
+
+
+def test_small_case_against_cpu_oracle_gemm(mods, golden):
+    s24 = mods["s24"]
+    ap = oracle.prune(golden["gemm_f16.A"], oracle.FP16)
+    vals, ml, e = oracle.compress(ap, oracle.FP16)
+    E = torch.from_numpy(e).to(DEV)
+    B = from_bits(golden["gemm_f16.B"], torch.float16, DEV)
+    C = mods["ws"].run_sparse_ws_matmul(from_bits(vals, torch.float16, DEV), E, B)
+    _status_ok(s24)
+    want32 = torch.from_numpy(golden["gemm_f16.C_f32"]).to(DEV)
+    _check(C, want32)
+    c32, _ = oracle.gemm_f32acc(ap, golden["gemm_f16.B"], oracle.FP16)
+    _check(C, torch.from_numpy(c32).to(DEV))
+
+
+def test_dropin_launcher_with_reference_layout_metadata(mods):
+    """config 1 of the benchmark: A 2048 x 2048, B 2048 x 8192, through
+    run_sparse_ws_matmul(A_vals, E, B) exactly as the reference's self-check calls it."""
+    s24 = mods["s24"]
+    M, K, N = 2048, 2048, 8192
+    A, B, ap, vals, ml, e = _prepare(M, K, N, torch.float16, 1234)
+    Av = from_bits(vals, torch.float16, DEV)
+    E = torch.from_numpy(e).to(DEV).view(M // 16, K)
+    C = mods["ws"].run_sparse_ws_matmul(Av, E, B.to(DEV))
+    _status_ok(s24)
+    _check(C, _reference(ap, B, torch.float16))
+    C2 = mods["ws"].run_sparse_ws_matmul(Av, E, B.to(DEV), tune=False,
+                                         manual_config={"BM": 128, "BN": 128, "BK": 64, "warps": 8, "buffers": 4, "SF": 4})
+    _check(C2, _reference(ap, B, torch.float16))
+
+
+def test_two_kernel_entry_point(mods):
+    """v11.1: dense A -> prune+compress kernel -> sparse GEMM; the metadata stays in the
+    tensor-core layout between the two launches."""
+    s24 = mods["s24"]
+    M, K, N = 1024, 1536, 2048
+    A = randn((M, K), torch.float16, 77)
+    B = randn((K, N), torch.float16, 78)
+    C = mods["two"].run_2_kernel_ws_matmul(A.to(DEV), B.to(DEV))
+    _status_ok(s24)
+    ap = oracle.prune(bits(A), oracle.FP16, oracle.MODE_SIGNED, oracle.TIE_HIGHER)
+    _check(C, _reference(ap, B, torch.float16))
+
+
+def test_bf16_weight_times_activation_shape(mods):
+    s24 = mods["s24"]
+    M, K, N = 1792, 1024, 4096      # a 1/16-scale slice of the MLP-shaped configuration
+    A = randn((M, K), torch.bfloat16, 5000, scale=0.02)
+    B = randn((K, N), torch.bfloat16, 5001)
+    vals, _, tc = s24.prune_compress(A.to(DEV), want_ref=False, want_tc=True)
+    C = s24.spmm(vals, tc, B.to(DEV))
+    _status_ok(s24)
+    ap = oracle.prune(bits(A), oracle.BF16)
+    ref = _reference(ap, B, torch.bfloat16)
+    torch.testing.assert_close(C.float(), ref, rtol=RTOL, atol=ATOL)
+
+
+def test_linearity_at_full_size(mods):
+    """8192^3 is too large for a CPU check: use C(B1 + B2) = C(B1) + C(B2) with small-integer
+    B (exact in fp16 and in the fp32 accumulator) and compare sampled rows with torch."""
+    s24 = mods["s24"]
+    M = N = K = 8192
+    g = torch.Generator(device=DEV).manual_seed(8192)
+    A = torch.randint(-3, 4, (M, K), generator=g, device=DEV).to(torch.float16)
+    B1 = torch.randint(-2, 3, (K, N), generator=g, device=DEV).to(torch.float16)
+    B2 = torch.randint(-2, 3, (K, N), generator=g, device=DEV).to(torch.float16)
+    vals, _, tc = s24.prune_compress(A, want_ref=False, want_tc=True)
+    C1 = s24.spmm(vals, tc, B1)
+    C2 = s24.spmm(vals, tc, B2)
+    C12 = s24.spmm(vals, tc, B1 + B2)
+    _status_ok(s24)
+    # integer sums of magnitude < 2048 * ... stay exactly representable only up to 2048 in fp16;
+    # compare in fp32 with one fp16 ulp of slack at the observed magnitude
+    tol = float(C12.float().abs().max()) * 2 ** -10
+    assert float((C12.float() - (C1.float() + C2.float())).abs().max()) <= 2 * tol + 1e-3
+    Ap = s24.prune(A)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8191], device=DEV)
+    ref = Ap[rows].float() @ B1.float()
+    torch.testing.assert_close(C1[rows].float(), ref.to(torch.float16).float(), rtol=RTOL, atol=ATOL)
