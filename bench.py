@@ -217,8 +217,11 @@ def run_ours(args, rank, world, local):
     C = torch.empty(GEMM_M, GEMM_N, dtype=torch.float16, device=dev)
     del A
 
+    from s24.multi import NShardedSpmm
+    op = NShardedSpmm(vals, tc, spmm_fn=lambda v, m, b, out=None: s24.spmm(v, m, b, out=C if out is None else out))
+
     def gemm_step():
-        s24.spmm(vals, tc, B, out=C)
+        op(B)          # this rank's column shard; no collective on the data path
 
     def barrier():
         if use_dist:
@@ -357,6 +360,30 @@ def run_ours(args, rank, world, local):
     return 0
 
 
+def run_profile_target(args):
+    """A bounded run of one kernel for profiler captures; prints no benchmark line."""
+    import s24
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(4000)
+    if args.profile_target == "gemm":
+        n = args.size or GEMM_M
+        A = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+        B = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+        vals, _, tc = s24.prune_compress(A, want_ref=False, want_tc=True)
+        C = torch.empty(n, n, dtype=torch.float16, device=dev)
+        fn = lambda: s24.spmm(vals, tc, B, out=C)  # noqa: E731
+    else:
+        n = args.size or PC_M
+        A = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+        fn = lambda: s24.prune_compress(A, want_ref=True, want_tc=False)  # noqa: E731
+    for _ in range(max(args.warmup, 1) + args.steps):
+        fn()
+    torch.cuda.synchronize(dev)
+    print(f"profile target {args.profile_target} n={n}: {max(args.warmup, 1) + args.steps} launches done")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -364,10 +391,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-target", choices=["gemm", "prune_compress"], default=None,
+                    help="for ncu captures: launch only this kernel (warm-up + --steps launches) and exit")
+    ap.add_argument("--size", type=int, default=0, help="with --profile-target: square problem size (default: the bench's)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
         return run_reference_arm(args, rank, world)
+    if args.profile_target:
+        return run_profile_target(args)
     if world == 1 and args.gpus > 1:
         # launched without torchrun: re-launch one rank per GPU
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

@@ -5,11 +5,13 @@ layout and error behaviour and runs on the B200 through libs24 (C ABI `s24_compr
 """
 import torch
 
-try:
-    from . import _paths  # noqa: F401
-except ImportError:
-    import _paths  # noqa: F401
-import s24
+import sys
+from pathlib import Path
+
+_PKG_ROOT = str(Path(__file__).resolve().parent.parent)   # makes `s24` importable however this file is loaded
+if _PKG_ROOT not in sys.path:
+    sys.path.insert(0, _PKG_ROOT)
+import s24  # noqa: E402
 
 
 def _calculate_meta_reordering_offsets(m, meta_ncols, device):

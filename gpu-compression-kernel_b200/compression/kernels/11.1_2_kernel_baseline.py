@@ -8,8 +8,9 @@ directly, 11.1_2_kernel_baseline.py:120-122,288-296).
 import sys
 from pathlib import Path
 
-sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
-import _paths  # noqa: F401,E402
+_PKG_ROOT = str(Path(__file__).resolve().parent.parent.parent)   # makes `s24` importable however this file is loaded
+if _PKG_ROOT not in sys.path:
+    sys.path.insert(0, _PKG_ROOT)
 import s24  # noqa: E402
 
 

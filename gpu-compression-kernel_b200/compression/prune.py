@@ -6,11 +6,13 @@ small torch utilities so that `from prune import *` keeps working.
 """
 import torch
 
-try:
-    from . import _paths  # noqa: F401
-except ImportError:  # flat import from this directory, as the reference's scripts do
-    import _paths  # noqa: F401
-import s24
+import sys
+from pathlib import Path
+
+_PKG_ROOT = str(Path(__file__).resolve().parent.parent)   # makes `s24` importable however this file is loaded
+if _PKG_ROOT not in sys.path:
+    sys.path.insert(0, _PKG_ROOT)
+import s24  # noqa: E402
 
 
 def gen_mask(device: torch.device, size: tuple, n: int, m: int):

@@ -53,29 +53,23 @@ struct PcParams {
     uint16_t* vals;    // (M, K/2)
     uint32_t* meta_ref;  // (M/16, K/2) words, may be null
     uint32_t* meta_tc;   // records, may be null
-    int mode, tie;
-    uint32_t keymask, force_keep, keep_zero_bits;
+    int tie;
     int64_t col_blocks;  // ceil(K / 128)
     int64_t warp_tiles;  // (M/16) * col_blocks
 };
 
 // 32 elements of one row -> 16 stored values + 32 metadata bits
-template <int DT>
-__device__ __forceinline__ uint32_t row_span(const uint32_t (&lo)[8], const uint32_t (&hi)[8], const PcParams& p,
-                                             uint32_t (&out)[8])
+template <int DT, int MODE>
+__device__ __forceinline__ uint32_t row_span(const uint32_t (&lo)[8], const uint32_t (&hi)[8], int tie, uint32_t (&out)[8])
 {
-    uint32_t c0 = prune_compress_8<DT>(lo[0], lo[1], lo[2], lo[3], p.mode, p.tie, p.keymask, p.force_keep,
-                                       p.keep_zero_bits, out[0], out[1]);
-    uint32_t c1 = prune_compress_8<DT>(lo[4], lo[5], lo[6], lo[7], p.mode, p.tie, p.keymask, p.force_keep,
-                                       p.keep_zero_bits, out[2], out[3]);
-    uint32_t c2 = prune_compress_8<DT>(hi[0], hi[1], hi[2], hi[3], p.mode, p.tie, p.keymask, p.force_keep,
-                                       p.keep_zero_bits, out[4], out[5]);
-    uint32_t c3 = prune_compress_8<DT>(hi[4], hi[5], hi[6], hi[7], p.mode, p.tie, p.keymask, p.force_keep,
-                                       p.keep_zero_bits, out[6], out[7]);
-    return c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+    const uint32_t c0 = prune_compress_8<DT, MODE>(lo[0], lo[1], lo[2], lo[3], tie, out[0], out[1]);
+    const uint32_t c1 = prune_compress_8<DT, MODE>(lo[4], lo[5], lo[6], lo[7], tie, out[2], out[3]);
+    const uint32_t c2 = prune_compress_8<DT, MODE>(hi[0], hi[1], hi[2], hi[3], tie, out[4], out[5]);
+    const uint32_t c3 = prune_compress_8<DT, MODE>(hi[4], hi[5], hi[6], hi[7], tie, out[6], out[7]);
+    return gather_code_bytes(c0, c1, c2, c3);
 }
 
-template <int DT, bool LD256>
+template <int DT, int MODE, bool LD256>
 __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
 {
     const int lane = threadIdx.x & 31;
@@ -104,8 +98,8 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
     }
 
     uint32_t va[8], vb[8];
-    const uint32_t ma = row_span<DT>(a_lo, a_hi, p, va);
-    const uint32_t mb = row_span<DT>(b_lo, b_hi, p, vb);
+    const uint32_t ma = row_span<DT, MODE>(a_lo, a_hi, p.tie, va);
+    const uint32_t mb = row_span<DT, MODE>(b_lo, b_hi, p.tie, vb);
 
     const int64_t half_k = p.K >> 1;
     st256(p.vals + rA * half_k + (col0 >> 1), va);
@@ -129,10 +123,9 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
 
 // ---------------------------------------------------------------- dense prune (prune_2_4)
 
-template <int DT, bool V128>
+template <int DT, int MODE, bool V128>
 __global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* __restrict__ A, uint16_t* __restrict__ out,
-                                                          int64_t numel, int mode, int tie, uint32_t keymask,
-                                                          uint32_t keep_zero_bits)
+                                                          int64_t numel, int tie)
 {
     const int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t base = i8 * 8;
@@ -150,7 +143,7 @@ __global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* __rest
             in[2] = w.x; in[3] = w.y;
         }
     }
-    prune_8<DT>(in[0], in[1], in[2], in[3], mode, tie, keymask, keep_zero_bits, o[0], o[1], o[2], o[3]);
+    prune_8<DT, MODE>(in[0], in[1], in[2], in[3], tie, o[0], o[1], o[2], o[3]);
     if (V128 && full) {
         *reinterpret_cast<uint4*>(out + base) = make_uint4(o[0], o[1], o[2], o[3]);
     } else {
@@ -225,24 +218,28 @@ static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld
     p.vals = static_cast<uint16_t*>(vals);
     p.meta_ref = static_cast<uint32_t*>(meta_ref);
     p.meta_tc = static_cast<uint32_t*>(meta_tc);
-    p.mode = mode;
     p.tie = tie;
-    p.keymask = mode == kModeMagnitude ? 0x7FFF7FFFu : 0xFFFFFFFFu;
-    p.force_keep = mode == kModeNone ? 0xFFFFFFFFu : 0u;
-    p.keep_zero_bits = mode == kModeMagnitude ? 0u : 0xFFFFFFFFu;
     p.col_blocks = (K + 127) / 128;
     p.warp_tiles = (M / 16) * p.col_blocks;
     const int64_t blocks = (p.warp_tiles + 7) / 8;
     if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "prune_compress: matrix too large for one launch");
     const bool ld256ok = aligned(A, 32) && (ld % 16 == 0);
     dim3 grid((unsigned)blocks), block(256);
-    if (dtype == S24_FP16) {
-        if (ld256ok) prune_compress_kernel<kFp16, true><<<grid, block, 0, stream>>>(p);
-        else prune_compress_kernel<kFp16, false><<<grid, block, 0, stream>>>(p);
-    } else {
-        if (ld256ok) prune_compress_kernel<kBf16, true><<<grid, block, 0, stream>>>(p);
-        else prune_compress_kernel<kBf16, false><<<grid, block, 0, stream>>>(p);
-    }
+#define S24_LAUNCH_PC(DT, MODE)                                                              \
+    do {                                                                                     \
+        if (ld256ok) prune_compress_kernel<DT, MODE, true><<<grid, block, 0, stream>>>(p);   \
+        else prune_compress_kernel<DT, MODE, false><<<grid, block, 0, stream>>>(p);          \
+    } while (0)
+#define S24_LAUNCH_PC_MODE(DT)                                        \
+    do {                                                              \
+        if (mode == kModeSigned) S24_LAUNCH_PC(DT, kModeSigned);      \
+        else if (mode == kModeMagnitude) S24_LAUNCH_PC(DT, kModeMagnitude); \
+        else S24_LAUNCH_PC(DT, kModeNone);                            \
+    } while (0)
+    if (dtype == S24_FP16) S24_LAUNCH_PC_MODE(kFp16);
+    else S24_LAUNCH_PC_MODE(kBf16);
+#undef S24_LAUNCH_PC_MODE
+#undef S24_LAUNCH_PC
     return check_cuda(cudaGetLastError(), "prune_compress launch");
 }
 
@@ -278,20 +275,24 @@ extern "C" int s24_prune(const void* A, void* out, int64_t numel, int dtype, int
     const int64_t threads = (numel + 7) / 8;
     const int64_t blocks = (threads + 255) / 256;
     if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "prune: tensor too large for one launch");
-    const uint32_t keymask = mode == kModeMagnitude ? 0x7FFF7FFFu : 0xFFFFFFFFu;
-    const uint32_t kz = mode == kModeMagnitude ? 0u : 0xFFFFFFFFu;
     const bool v128 = aligned(A, 16) && aligned(out, 16);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint16_t* a = static_cast<const uint16_t*>(A);
     uint16_t* o = static_cast<uint16_t*>(out);
     dim3 grid((unsigned)blocks), block(256);
+#define S24_LAUNCH_PRUNE(DT, MODE)                                                          \
+    do {                                                                                    \
+        if (v128) prune_dense_kernel<DT, MODE, true><<<grid, block, 0, s>>>(a, o, numel, tie);  \
+        else prune_dense_kernel<DT, MODE, false><<<grid, block, 0, s>>>(a, o, numel, tie);      \
+    } while (0)
     if (dtype == S24_FP16) {
-        if (v128) prune_dense_kernel<kFp16, true><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
-        else prune_dense_kernel<kFp16, false><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
+        if (mode == kModeMagnitude) S24_LAUNCH_PRUNE(kFp16, kModeMagnitude);
+        else S24_LAUNCH_PRUNE(kFp16, kModeSigned);
     } else {
-        if (v128) prune_dense_kernel<kBf16, true><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
-        else prune_dense_kernel<kBf16, false><<<grid, block, 0, s>>>(a, o, numel, mode, tie, keymask, kz);
+        if (mode == kModeMagnitude) S24_LAUNCH_PRUNE(kBf16, kModeMagnitude);
+        else S24_LAUNCH_PRUNE(kBf16, kModeSigned);
     }
+#undef S24_LAUNCH_PRUNE
     return check_cuda(cudaGetLastError(), "prune launch");
 }
 

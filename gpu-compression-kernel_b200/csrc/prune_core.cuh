@@ -97,13 +97,49 @@ S24_HD uint32_t eq2(uint32_t a, uint32_t b)
 #endif
 }
 
+// per-half max / min of packed 16-bit floats (either operand may be returned for +0 / -0)
+template <int DT>
+S24_HD uint32_t max2(uint32_t a, uint32_t b)
+{
+#if defined(__CUDA_ARCH__)
+    if (DT == kBf16) {
+        __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    __half2 r = __hmax2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+#else
+    uint32_t lo = bits_to_float(a & 0xFFFF, DT) >= bits_to_float(b & 0xFFFF, DT) ? (a & 0xFFFFu) : (b & 0xFFFFu);
+    uint32_t hi = bits_to_float(a >> 16, DT) >= bits_to_float(b >> 16, DT) ? (a & 0xFFFF0000u) : (b & 0xFFFF0000u);
+    return lo | hi;
+#endif
+}
+
+template <int DT>
+S24_HD uint32_t min2(uint32_t a, uint32_t b)
+{
+#if defined(__CUDA_ARCH__)
+    if (DT == kBf16) {
+        __nv_bfloat162 r = __hmin2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    __half2 r = __hmin2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+#else
+    uint32_t lo = bits_to_float(a & 0xFFFF, DT) <= bits_to_float(b & 0xFFFF, DT) ? (a & 0xFFFFu) : (b & 0xFFFFu);
+    uint32_t hi = bits_to_float(a >> 16, DT) <= bits_to_float(b >> 16, DT) ? (a & 0xFFFF0000u) : (b & 0xFFFF0000u);
+    return lo | hi;
+#endif
+}
+
 // non-zero flags; +0.0 and -0.0 are both "zero" (dense != 0, compress_2_4.py:72)
+template <int DT>
 S24_HD uint32_t nz2(uint32_t a)
 {
 #if defined(__CUDA_ARCH__)
-    // an fp16 compare against +0.0; bf16 zeros have the same two bit patterns
-    uint32_t m = a & 0x7FFF7FFFu;  // (also keeps NaN payloads from comparing unordered)
-    return __vcmpne2(m, 0u);
+    uint32_t zero = 0;
+    if (DT == kBf16) return __hne2_mask(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&zero));
+    return __hne2_mask(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&zero));
 #else
     uint32_t m = a & 0x7FFF7FFFu;
     return ((m & 0xFFFFu) ? 0xFFFFu : 0u) | ((m >> 16) ? 0xFFFF0000u : 0u);
@@ -111,41 +147,37 @@ S24_HD uint32_t nz2(uint32_t a)
 }
 
 S24_HD uint32_t sel(uint32_t mask, uint32_t a, uint32_t b) { return (a & mask) | (b & ~mask); }
-S24_HD uint32_t maj(uint32_t a, uint32_t b, uint32_t c) { return (a & b) | (a & c) | (b & c); }
 
 // ---------------------------------------------------------------- encoder (shared)
 
-// From keep masks and the elements, produce the two stored values of each group and the
-// 4-bit codes.  pm_j marks the elements that survive pruning with their bits intact, m_j
-// the survivors that are also non-zero (the flags the reference's encoder sees).
-//   V0/V1: stored value 0 / 1 of group G (low half) and G+1 (high half)
+// From the surviving elements p_j (dropped ones already zeroed) produce the two stored values
+// of each group and the 4-bit codes, exactly as compress_2_4.py:113-131 does from the
+// non-zero flags m_j = (p_j != 0):
+//   idx0 = 0 if m0, 1 if !m0 & m1, else 2;  idx1 = 1 if m0 & m1, 3 if (!m0 & !m1) | m3, else 2
+//   code = idx0 | idx1 << 2, which over (m0, m1) reads 0100 / 1001 / 1000 / 1110 for
+//   (1,1) / (0,1) / (1,0) / (0,0), with bit 2 also set by m3.
+//   v0/v1: stored value 0 / 1 of group G (low half) and G+1 (high half)
 //   codes: bits 0-3 code of group G, bits 16-19 code of group G+1
 struct PairOut {
     uint32_t v0, v1, codes;
 };
 
-S24_HD PairOut encode_pair(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3,
-                           uint32_t k0, uint32_t k1, uint32_t k2, uint32_t k3, uint32_t keep_zero_bits)
+template <int DT, bool ZERO_SIGN_CLEAR>
+S24_HD PairOut encode_pair(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3)
 {
-    // keep_zero_bits = ~0 : a surviving zero keeps its bit pattern (signed mode, -0.0 stays)
-    //                =  0 : surviving zeros read +0.0 (magnitude mode)
-    uint32_t n0 = nz2(P0), n1 = nz2(P1), n2 = nz2(P2), n3 = nz2(P3);
-    uint32_t p0 = P0 & k0 & (n0 | keep_zero_bits);
-    uint32_t p1 = P1 & k1 & (n1 | keep_zero_bits);
-    uint32_t p2 = P2 & k2 & (n2 | keep_zero_bits);
-    uint32_t p3 = P3 & k3 & (n3 | keep_zero_bits);
-    uint32_t m0 = k0 & n0, m1 = k1 & n1, m3 = k3 & n3;
-    (void)n2;
-    // compress_2_4.py:113-121
-    uint32_t both = m0 & m1;        // expr0
-    uint32_t only1 = ~m0 & m1;      // expr1 -> bit0
-    uint32_t none = ~(m0 | m1);     // expr2 -> bit1
-    uint32_t bit2 = both | none | m3;
-    uint32_t bit3 = ~both;          // expr1 | ~m1
+    const uint32_t m0 = nz2<DT>(p0), m1 = nz2<DT>(p1), m3 = nz2<DT>(p3);
+    if (ZERO_SIGN_CLEAR) {  // magnitude mode: a surviving -0.0 reads +0.0
+        p0 &= m0;
+        p1 &= m1;
+        p2 &= nz2<DT>(p2);
+        p3 &= m3;
+    }
+    const uint32_t both = m0 & m1;
+    const uint32_t none_or_m3 = ~(m0 | m1) | m3;
     PairOut o;
-    o.v0 = sel(m0, p0, sel(m1, p1, p2));                    // idx0 in {0,1,2}
-    o.v1 = sel(both, p1, sel(none | m3, p3, p2));           // idx1 in {1,2,3}
-    o.codes = (only1 & 0x00010001u) | (none & 0x00020002u) | (bit2 & 0x00040004u) | (bit3 & 0x00080008u);
+    o.v0 = sel(m0, p0, sel(m1, p1, p2));
+    o.v1 = sel(both, p1, sel(none_or_m3, p3, p2));
+    o.codes = ((0x000E000Eu ^ (m0 & 0x00060006u)) ^ (m1 & 0x00070007u) ^ (both & 0x000B000Bu)) | (m3 & 0x00040004u);
     return o;
 }
 
@@ -186,122 +218,107 @@ S24_HD uint32_t keep_mask_scalar(const float k[4], int tie)
 
 // ---------------------------------------------------------------- the packed fast path
 
-// Result of pruning + encoding two groups.  tie != 0 in a half means that group has a key
-// tie across the keep / drop boundary and must be redone with keep_mask_scalar.
-struct PairResult {
-    uint32_t v0, v1, codes, tie;
-};
-
-// keymask: 0xFFFFFFFF signed keys, 0x7FFF7FFF magnitude keys.
-// force_keep: 0xFFFFFFFF turns pruning off (compress-only), else 0.
-template <int DT>
-S24_HD PairResult prune_encode_pair(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3,
-                                    uint32_t keymask, uint32_t force_keep, uint32_t keep_zero_bits)
+// Keep masks of two groups at once.  The second and third largest keys of a group are the
+// two "middle" elements {min(max(a0,a1), max(a2,a3)), max(min(a0,a1), min(a2,a3))}; an
+// element survives when its key reaches the second largest.  That is exact unless second ==
+// third (a tie across the keep/drop boundary), which `tie` reports per half so that the
+// group can be redone with keep_mask_scalar.  All comparisons are fp16/bf16 SIMD compares.
+template <int DT, int MODE>
+S24_HD void keep_masks(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, uint32_t& k0, uint32_t& k1, uint32_t& k2,
+                       uint32_t& k3, uint32_t& tie)
 {
-    uint32_t K0 = P0 & keymask, K1 = P1 & keymask, K2 = P2 & keymask, K3 = P3 & keymask;
-    uint32_t g01 = ge2<DT>(K0, K1), g02 = ge2<DT>(K0, K2), g03 = ge2<DT>(K0, K3);
-    uint32_t g12 = ge2<DT>(K1, K2), g13 = ge2<DT>(K1, K3), g23 = ge2<DT>(K2, K3);
-    // element i survives when it beats at least two others; i beats j>i on >=, j beats i on >
-    uint32_t k0 = maj(g01, g02, g03);
-    uint32_t k1 = maj(~g01, g12, g13);
-    uint32_t k2 = maj(~g02, ~g12, g23);
-    uint32_t k3 = maj(~g03, ~g13, ~g23);
-    uint32_t e01 = eq2<DT>(K0, K1), e02 = eq2<DT>(K0, K2), e03 = eq2<DT>(K0, K3);
-    uint32_t e12 = eq2<DT>(K1, K2), e13 = eq2<DT>(K1, K3), e23 = eq2<DT>(K2, K3);
-    uint32_t tie = (e01 & (k0 ^ k1)) | (e02 & (k0 ^ k2)) | (e03 & (k0 ^ k3)) |
-                   (e12 & (k1 ^ k2)) | (e13 & (k1 ^ k3)) | (e23 & (k2 ^ k3));
-    PairOut o = encode_pair(P0, P1, P2, P3, k0 | force_keep, k1 | force_keep, k2 | force_keep,
-                            k3 | force_keep, keep_zero_bits);
-    PairResult r;
-    r.v0 = o.v0;
-    r.v1 = o.v1;
-    r.codes = o.codes;
-    r.tie = tie & ~force_keep;
-    return r;
+    if (MODE == kModeNone) {
+        k0 = k1 = k2 = k3 = 0xFFFFFFFFu;
+        tie = 0;
+        return;
+    }
+    const uint32_t km = MODE == kModeMagnitude ? 0x7FFF7FFFu : 0xFFFFFFFFu;
+    const uint32_t K0 = P0 & km, K1 = P1 & km, K2 = P2 & km, K3 = P3 & km;
+    const uint32_t hi01 = max2<DT>(K0, K1), lo01 = min2<DT>(K0, K1);
+    const uint32_t hi23 = max2<DT>(K2, K3), lo23 = min2<DT>(K2, K3);
+    const uint32_t x = min2<DT>(hi01, hi23), y = max2<DT>(lo01, lo23);
+    const uint32_t second = max2<DT>(x, y);
+    tie = eq2<DT>(x, y);
+    k0 = ge2<DT>(K0, second);
+    k1 = ge2<DT>(K1, second);
+    k2 = ge2<DT>(K2, second);
+    k3 = ge2<DT>(K3, second);
 }
 
-// Redo one group (half = 0 low / 1 high of the packed registers) with the scalar tie rule
-// and patch the packed outputs.
-template <int DT>
-S24_HD void fix_tied_group(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, int half, int mode, int tie,
-                           PairResult& r)
+// scalar redo of one group (half = 0 low / 1 high of the packed registers): keep mask bits
+template <int DT, int MODE>
+S24_HD uint32_t scalar_keep(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, int half, int tie)
 {
     const int sh = 16 * half;
+    const uint32_t e[4] = {(P0 >> sh) & 0xFFFFu, (P1 >> sh) & 0xFFFFu, (P2 >> sh) & 0xFFFFu, (P3 >> sh) & 0xFFFFu};
     float k[4];
-    uint32_t e[4] = {(P0 >> sh) & 0xFFFFu, (P1 >> sh) & 0xFFFFu, (P2 >> sh) & 0xFFFFu, (P3 >> sh) & 0xFFFFu};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        float v = bits_to_float(e[i], DT);
-        k[i] = (mode == kModeMagnitude) ? (v < 0.f ? -v : v) : v;
+        const float v = bits_to_float(e[i], DT);
+        k[i] = (MODE == kModeMagnitude) ? (v < 0.f ? -v : v) : v;
     }
-    uint32_t m = keep_mask_scalar(k, tie);
-    uint32_t hm = 0xFFFFu << sh;
-    uint32_t k0 = (m & 1u) ? hm : 0u, k1 = (m & 2u) ? hm : 0u, k2 = (m & 4u) ? hm : 0u, k3 = (m & 8u) ? hm : 0u;
-    PairOut o = encode_pair(P0 & hm, P1 & hm, P2 & hm, P3 & hm, k0, k1, k2, k3,
-                            mode == kModeMagnitude ? 0u : 0xFFFFFFFFu);
-    r.v0 = (r.v0 & ~hm) | (o.v0 & hm);
-    r.v1 = (r.v1 & ~hm) | (o.v1 & hm);
-    r.codes = (r.codes & ~hm) | (o.codes & hm);
+    return keep_mask_scalar(k, tie);
+}
+
+template <int DT, int MODE>
+S24_HD void fix_tied_masks(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, uint32_t tiebits, int tie, uint32_t& k0,
+                           uint32_t& k1, uint32_t& k2, uint32_t& k3)
+{
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const uint32_t hm = 0xFFFFu << (16 * half);
+        if ((tiebits & hm) == 0) continue;
+        const uint32_t m = scalar_keep<DT, MODE>(P0, P1, P2, P3, half, tie);
+        k0 = (k0 & ~hm) | ((m & 1u) ? hm : 0u);
+        k1 = (k1 & ~hm) | ((m & 2u) ? hm : 0u);
+        k2 = (k2 & ~hm) | ((m & 4u) ? hm : 0u);
+        k3 = (k3 & ~hm) | ((m & 8u) ? hm : 0u);
+    }
 }
 
 // Complete treatment of 8 consecutive elements (two groups) held as four registers in
 // memory order: in0 = (a0,a1) of group G, in1 = (a2,a3) of G, in2 = (a0,a1) of G+1, in3.
 //   out_lo / out_hi : the 4 stored values in memory order (v0_G, v1_G) / (v0_G+1, v1_G+1)
-//   returns the two 4-bit codes as one byte: code_G | code_G+1 << 4
-template <int DT>
-S24_HD uint32_t prune_compress_8(uint32_t in0, uint32_t in1, uint32_t in2, uint32_t in3, int mode, int tie,
-                                 uint32_t keymask, uint32_t force_keep, uint32_t keep_zero_bits,
-                                 uint32_t& out_lo, uint32_t& out_hi)
+//   returns a word whose top byte is code_G | code_G+1 << 4 (lower bytes are scratch)
+template <int DT, int MODE>
+S24_HD uint32_t prune_compress_8(uint32_t in0, uint32_t in1, uint32_t in2, uint32_t in3, int tie, uint32_t& out_lo,
+                                 uint32_t& out_hi)
 {
-    uint32_t P0 = byte_perm(in0, in2, 0x5410), P1 = byte_perm(in0, in2, 0x7632);
-    uint32_t P2 = byte_perm(in1, in3, 0x5410), P3 = byte_perm(in1, in3, 0x7632);
-    PairResult r = prune_encode_pair<DT>(P0, P1, P2, P3, keymask, force_keep, keep_zero_bits);
-    if (r.tie != 0 && tie != kTieLower) {  // rare: a tie across the keep/drop boundary
-        if (r.tie & 0xFFFFu) fix_tied_group<DT>(P0, P1, P2, P3, 0, mode, tie, r);
-        if (r.tie >> 16) fix_tied_group<DT>(P0, P1, P2, P3, 1, mode, tie, r);
-    }
-    out_lo = byte_perm(r.v0, r.v1, 0x5410);
-    out_hi = byte_perm(r.v0, r.v1, 0x7632);
-    return (r.codes & 0xFu) | ((r.codes >> 12) & 0xF0u);
+    const uint32_t P0 = byte_perm(in0, in2, 0x5410), P1 = byte_perm(in0, in2, 0x7632);
+    const uint32_t P2 = byte_perm(in1, in3, 0x5410), P3 = byte_perm(in1, in3, 0x7632);
+    uint32_t k0, k1, k2, k3, tiebits;
+    keep_masks<DT, MODE>(P0, P1, P2, P3, k0, k1, k2, k3, tiebits);
+    if (tiebits != 0) fix_tied_masks<DT, MODE>(P0, P1, P2, P3, tiebits, tie, k0, k1, k2, k3);  // rare
+    const PairOut o = encode_pair<DT, MODE == kModeMagnitude>(P0 & k0, P1 & k1, P2 & k2, P3 & k3);
+    out_lo = byte_perm(o.v0, o.v1, 0x5410);
+    out_hi = byte_perm(o.v0, o.v1, 0x7632);
+    // codes = lo + hi * 2^16; times (2^24 + 2^12) puts lo at bits 24-27 and hi at bits 28-31
+    return o.codes * 0x01001000u;
 }
 
-// Keep masks only (dense prune output): returns the 8 elements with dropped ones zeroed.
-template <int DT>
-S24_HD void prune_8(uint32_t in0, uint32_t in1, uint32_t in2, uint32_t in3, int mode, int tie, uint32_t keymask,
-                    uint32_t keep_zero_bits, uint32_t& o0, uint32_t& o1, uint32_t& o2, uint32_t& o3)
+// gather the top bytes of four such words into one 32-bit metadata word
+S24_HD uint32_t gather_code_bytes(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3)
 {
-    uint32_t P0 = byte_perm(in0, in2, 0x5410), P1 = byte_perm(in0, in2, 0x7632);
-    uint32_t P2 = byte_perm(in1, in3, 0x5410), P3 = byte_perm(in1, in3, 0x7632);
-    uint32_t K0 = P0 & keymask, K1 = P1 & keymask, K2 = P2 & keymask, K3 = P3 & keymask;
-    uint32_t g01 = ge2<DT>(K0, K1), g02 = ge2<DT>(K0, K2), g03 = ge2<DT>(K0, K3);
-    uint32_t g12 = ge2<DT>(K1, K2), g13 = ge2<DT>(K1, K3), g23 = ge2<DT>(K2, K3);
-    uint32_t k0 = maj(g01, g02, g03), k1 = maj(~g01, g12, g13), k2 = maj(~g02, ~g12, g23), k3 = maj(~g03, ~g13, ~g23);
-    uint32_t e01 = eq2<DT>(K0, K1), e02 = eq2<DT>(K0, K2), e03 = eq2<DT>(K0, K3);
-    uint32_t e12 = eq2<DT>(K1, K2), e13 = eq2<DT>(K1, K3), e23 = eq2<DT>(K2, K3);
-    uint32_t tiebits = (e01 & (k0 ^ k1)) | (e02 & (k0 ^ k2)) | (e03 & (k0 ^ k3)) |
-                       (e12 & (k1 ^ k2)) | (e13 & (k1 ^ k3)) | (e23 & (k2 ^ k3));
-    if (tiebits != 0 && tie != kTieLower) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int sh = 16 * half;
-            if (((tiebits >> sh) & 0xFFFFu) == 0) continue;
-            float k[4];
-            uint32_t e[4] = {(P0 >> sh) & 0xFFFFu, (P1 >> sh) & 0xFFFFu, (P2 >> sh) & 0xFFFFu, (P3 >> sh) & 0xFFFFu};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float v = bits_to_float(e[i], DT);
-                k[i] = (mode == kModeMagnitude) ? (v < 0.f ? -v : v) : v;
-            }
-            uint32_t m = keep_mask_scalar(k, tie);
-            uint32_t hm = 0xFFFFu << sh;
-            k0 = (k0 & ~hm) | ((m & 1u) ? hm : 0u);
-            k1 = (k1 & ~hm) | ((m & 2u) ? hm : 0u);
-            k2 = (k2 & ~hm) | ((m & 4u) ? hm : 0u);
-            k3 = (k3 & ~hm) | ((m & 8u) ? hm : 0u);
-        }
+    return byte_perm(byte_perm(c0, c1, 0x0073), byte_perm(c2, c3, 0x0073), 0x5410);
+}
+
+// Keep masks only (dense prune output): the 8 elements with dropped ones zeroed.
+template <int DT, int MODE>
+S24_HD void prune_8(uint32_t in0, uint32_t in1, uint32_t in2, uint32_t in3, int tie, uint32_t& o0, uint32_t& o1,
+                    uint32_t& o2, uint32_t& o3)
+{
+    const uint32_t P0 = byte_perm(in0, in2, 0x5410), P1 = byte_perm(in0, in2, 0x7632);
+    const uint32_t P2 = byte_perm(in1, in3, 0x5410), P3 = byte_perm(in1, in3, 0x7632);
+    uint32_t k0, k1, k2, k3, tiebits;
+    keep_masks<DT, MODE>(P0, P1, P2, P3, k0, k1, k2, k3, tiebits);
+    if (tiebits != 0) fix_tied_masks<DT, MODE>(P0, P1, P2, P3, tiebits, tie, k0, k1, k2, k3);
+    uint32_t p0 = P0 & k0, p1 = P1 & k1, p2 = P2 & k2, p3 = P3 & k3;
+    if (MODE == kModeMagnitude) {  // defined as where(prune(|A|) != 0, A, 0): surviving -0.0 reads +0.0
+        p0 &= nz2<DT>(p0);
+        p1 &= nz2<DT>(p1);
+        p2 &= nz2<DT>(p2);
+        p3 &= nz2<DT>(p3);
     }
-    uint32_t p0 = P0 & k0 & (nz2(P0) | keep_zero_bits), p1 = P1 & k1 & (nz2(P1) | keep_zero_bits);
-    uint32_t p2 = P2 & k2 & (nz2(P2) | keep_zero_bits), p3 = P3 & k3 & (nz2(P3) | keep_zero_bits);
     o0 = byte_perm(p0, p1, 0x5410);
     o2 = byte_perm(p0, p1, 0x7632);
     o1 = byte_perm(p2, p3, 0x5410);

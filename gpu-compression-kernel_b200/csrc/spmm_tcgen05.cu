@@ -29,7 +29,6 @@
 
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
-#include <stdlib.h>
 
 namespace s24 {
 
@@ -43,8 +42,9 @@ constexpr int kGroupM = 8;          // M-tiles per raster group (compression/com
 constexpr int kThreads = 192;       // producer warp, MMA warp, 4 epilogue warps
 constexpr uint32_t kTmemCols = 512;
 
-template <int G, int BN, int STAGES>
+template <int G, int BN, int STAGES, bool PRUNE_OUT = false>
 struct GemmCfg {
+    static constexpr bool kPruneOut = PRUNE_OUT;
     static constexpr int kG = G;
     static constexpr int kBN = BN;
     static constexpr int kStages = STAGES;
@@ -59,6 +59,7 @@ struct GemmCfg {
     static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static_assert(kECol0 + 4 * STAGES <= (int)kTmemCols, "tensor memory budget");
     static_assert(kBNCta % 64 == 0, "B is loaded in 64-column swizzle atoms");
+    static_assert(kSmemBytes <= 232448, "shared memory budget (227 KB per CTA)");
 };
 
 struct GemmParams {
@@ -66,7 +67,6 @@ struct GemmParams {
     int64_t ldc;
     int M, N, K;
     int bf16;
-    int e_variant;   // bring-up switch for how the metadata column is addressed (0 = default)
     int* status;
     // fused output prune (unused by the plain kernel)
     void* c_vals;
@@ -99,6 +99,20 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int bf16)
     }
     __half2 v = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 2:4 prune of four fp32 accumulators along N, as the reference's fused epilogue does
+// (compression/kernels/10.1_prune_acc.py:100-117): signed keys, >= so the lower index survives
+// a tie, the two survivors in index order and the code derived from the keep mask.
+__device__ __forceinline__ uint32_t prune_group_f32(float a0, float a1, float a2, float a3, float& v0, float& v1)
+{
+    const bool c01 = a0 >= a1, c02 = a0 >= a2, c03 = a0 >= a3, c12 = a1 >= a2, c13 = a1 >= a3, c23 = a2 >= a3;
+    const bool b0 = (c01 && (c02 || c03)) || (c02 && c03);
+    const bool b1 = (!c01 && (c12 || c13)) || (c12 && c13);
+    const bool b2 = (!c02 && (!c12 || c23)) || (!c12 && c23);
+    v0 = b0 ? a0 : (b1 ? a1 : a2);
+    v1 = (b0 && b1) ? a1 : ((b2 && (b0 || b1)) ? a2 : a3);
+    return b0 ? (b1 ? 4u : (b2 ? 8u : 12u)) : (b1 ? (b2 ? 9u : 13u) : 14u);
 }
 
 template <class Cfg>
@@ -235,11 +249,9 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     for (int j = 0; j < 4; ++j) {
                         // K = 32 per instruction: 32 bytes further along A's rows, 32 k-rows (4096 B) into B,
                         // metadata column j (even column address + selector bit)
-                        uint32_t sel = (uint32_t)(j & 1), ecol = e_cols + (uint32_t)(j & 2);
-                        if (p.e_variant == 1) { sel = 0; ecol = e_cols + (uint32_t)j; }
-                        else if (p.e_variant == 2) { sel = (uint32_t)j; ecol = e_cols; }
                         tc_mma_sp_f16<G>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 256),
-                                         idesc | sel, ecol, (kb | j) != 0 ? 1u : 0u);
+                                         idesc | (uint32_t)(j & 1), e_cols + (uint32_t)(j & 2),
+                                         (kb | j) != 0 ? 1u : 0u);
                     }
                     if (G == 2) tc_commit_pair(bar_empty + 8 * s, 3);
                     else tc_commit<1>(bar_empty + 8 * s);
@@ -266,33 +278,107 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             }
             tc_fence_after();
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
-            uint32_t packed[BN / 2];
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    packed[c * 16 + i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), p.bf16);
-            }
-            // accumulator is in registers: hand the TMEM stage back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
-            if (++a == ACC) { a = 0; acc_phase ^= 1u; }
-
             const int64_t row = (int64_t)(tm * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
             const int col0 = tn * BN;
-            if (row < p.M) {
-                uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
+            if constexpr (!Cfg::kPruneOut) {
+                uint32_t packed[BN / 2];
 #pragma unroll
-                for (int c8 = 0; c8 < BN / 8; ++c8) {
-                    if (col0 + c8 * 8 < p.N)
-                        *reinterpret_cast<uint4*>(crow + c8 * 8) =
-                            make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        packed[c * 16 + i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), p.bf16);
+                }
+                // accumulator is in registers: hand the TMEM stage back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+
+                if (row < p.M) {
+                    uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
+#pragma unroll
+                    for (int c8 = 0; c8 < BN / 8; ++c8) {
+                        if (col0 + c8 * 8 < p.N)
+                            *reinterpret_cast<uint4*>(crow + c8 * 8) =
+                                make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
+                    }
+                }
+            } else {
+                // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
+                uint32_t vals[BN / 4];   // packed 16-bit pairs: 8 registers per 32 columns
+                uint32_t meta[BN / 32];  // codes of 8 groups, group g in bits 4g..4g+3
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
+                    tc_wait_ld();
+                    uint32_t m = 0;
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        float v0, v1;
+                        const uint32_t code = prune_group_f32(__uint_as_float(r[4 * g4]), __uint_as_float(r[4 * g4 + 1]),
+                                                              __uint_as_float(r[4 * g4 + 2]), __uint_as_float(r[4 * g4 + 3]), v0, v1);
+                        vals[c * 8 + g4] = pack2(v0, v1, p.bf16);   // rounded after selection (10.1_prune_acc.py:241)
+                        m |= code << (4 * g4);
+                    }
+                    meta[c] = m;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+
+                const bool row_ok = row < p.M;
+                if (row_ok) {
+                    uint16_t* vrow = static_cast<uint16_t*>(p.c_vals) + row * (int64_t)(p.N / 2) + col0 / 2;
+#pragma unroll
+                    for (int c = 0; c < BN / 32; ++c) {
+                        if (col0 + c * 32 < p.N) {
+                            *reinterpret_cast<uint4*>(vrow + c * 16) =
+                                make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
+                            *reinterpret_cast<uint4*>(vrow + c * 16 + 8) =
+                                make_uint4(vals[c * 8 + 4], vals[c * 8 + 5], vals[c * 8 + 6], vals[c * 8 + 7]);
+                        }
+                    }
+                }
+                // metadata words pair row r (low half) with row r+8 (high half): lanes l and l^8 of this
+                // warp.  Per 64 columns the lane with bit 3 clear assembles the two words of the first 32
+                // columns, its partner those of the second 32, so each writes 8 adjacent bytes.
+                const bool upper = (lane & 8) != 0;
+                const int m0 = lane & 7;
+                const int64_t row16 = row >> 4;
+#pragma unroll
+                for (int c2 = 0; c2 < BN / 64; ++c2) {
+                    const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2], 8);
+                    const uint32_t xb = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2 + 1], 8);
+                    uint32_t w0, w1;  // logical columns c and c+1 (16 columns each) of rows (r, r+8)
+                    if (!upper) {
+                        w0 = __byte_perm(meta[2 * c2], xa, 0x5410);
+                        w1 = __byte_perm(meta[2 * c2], xa, 0x7632);
+                    } else {
+                        w0 = __byte_perm(xb, meta[2 * c2 + 1], 0x5410);
+                        w1 = __byte_perm(xb, meta[2 * c2 + 1], 0x7632);
+                    }
+                    const int ncol = col0 + c2 * 64 + (upper ? 32 : 0);   // first column these two words describe
+                    if (row_ok && ncol < p.N) {
+                        const int cidx = ncol >> 4;                        // logical metadata column of w0
+                        if (p.c_meta_ref != nullptr) {
+                            uint32_t* e = p.c_meta_ref + row16 * (int64_t)(p.N / 2) + (cidx >> 2) * 32 + m0 * 4 + (cidx & 3);
+                            *reinterpret_cast<uint2*>(e) = make_uint2(w0, w1);
+                        }
+                        if (p.c_meta_tc != nullptr) {
+                            const int64_t t128 = row >> 7;
+                            const int m2 = (int)((row >> 4) & 7);
+                            const int kb = cidx >> 3, j = (cidx & 7) >> 1;
+                            uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)(p.N >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
+                            rec[0] = w0;
+                            rec[32] = w1;
+                        }
+                    }
                 }
             }
+            if (++a == ACC) { a = 0; acc_phase ^= 1u; }
         }
     }
 
@@ -407,21 +493,26 @@ static int* status_word_address()
 }
 
 static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* C, int64_t M, int64_t N, int64_t K,
-                    int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, cudaStream_t stream)
+                    int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, cudaStream_t stream,
+                    bool prune_out = false, void* c_vals = nullptr, void* c_meta_ref = nullptr, void* c_meta_tc = nullptr)
 {
-    if (vals == nullptr || meta_tc == nullptr || B == nullptr || C == nullptr)
-        return fail(S24_ERR_INVALID_ARG, "spmm: null pointer");
-    if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "spmm: bad dtype %d", dtype);
+    const char* who = prune_out ? "spmm_prune_out" : "spmm";
+    if (vals == nullptr || meta_tc == nullptr || B == nullptr || (!prune_out && C == nullptr) || (prune_out && c_vals == nullptr))
+        return fail(S24_ERR_INVALID_ARG, "%s: null pointer", who);
+    if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "%s: bad dtype %d", who, dtype);
     if (M <= 0 || N <= 0 || K <= 0 || M % 128 != 0 || K % 128 != 0 || N % 8 != 0)
-        return fail(S24_ERR_SHAPE, "spmm: needs M %% 128 == 0, K %% 128 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)",
+        return fail(S24_ERR_SHAPE, "%s: needs M %% 128 == 0, K %% 128 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)", who,
                     (long long)M, (long long)N, (long long)K);
-    if (M > 0x7FFFFF00ll || N > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return fail(S24_ERR_SHAPE, "spmm: dimension too large");
-    if (ldb < N || ldb % 8 != 0 || ldc < N || ldc % 8 != 0)
-        return fail(S24_ERR_SHAPE, "spmm: ldb/ldc must be >= N and multiples of 8 (got %lld, %lld)", (long long)ldb, (long long)ldc);
-    if (!aligned(vals, 16) || !aligned(meta_tc, 16) || !aligned(B, 16) || !aligned(C, 16))
-        return fail(S24_ERR_INVALID_ARG, "spmm: pointers must be 16-byte aligned");
+    if (prune_out && N % 128 != 0)
+        return fail(S24_ERR_SHAPE, "%s: needs N %% 128 == 0 (got N=%lld)", who, (long long)N);
+    if (M > 0x7FFFFF00ll || N > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return fail(S24_ERR_SHAPE, "%s: dimension too large", who);
+    if (ldb < N || ldb % 8 != 0 || (!prune_out && (ldc < N || ldc % 8 != 0)))
+        return fail(S24_ERR_SHAPE, "%s: ldb/ldc must be >= N and multiples of 8 (got %lld, %lld)", who, (long long)ldb, (long long)ldc);
+    if (!aligned(vals, 16) || !aligned(meta_tc, 16) || !aligned(B, 16) || !aligned(C, 16) || !aligned(c_vals, 16) ||
+        !aligned(c_meta_ref, 16) || !aligned(c_meta_tc, 16))
+        return fail(S24_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", who);
     int* status = status_word_address();
-    if (status == nullptr) return fail(S24_ERR_CUDA, "spmm: cannot resolve the device status word");
+    if (status == nullptr) return fail(S24_ERR_CUDA, "%s: cannot resolve the device status word", who);
 
     GemmArgs g;
     g.vals = vals;
@@ -438,22 +529,24 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.N = (int)N;
     g.p.K = (int)K;
     g.p.bf16 = dtype == S24_BF16;
-    {
-        const char* v = getenv("S24_E_VARIANT");
-        g.p.e_variant = v ? atoi(v) : 0;
-    }
     g.p.status = status;
-    g.p.c_vals = nullptr;
-    g.p.c_meta_ref = nullptr;
-    g.p.c_meta_tc = nullptr;
+    g.p.c_vals = c_vals;
+    g.p.c_meta_ref = static_cast<uint32_t*>(c_meta_ref);
+    g.p.c_meta_tc = static_cast<uint32_t*>(c_meta_tc);
 
     int bm = cfg ? cfg->bm : 0, bn = cfg ? cfg->bn : 0;
     if (bm == 0) bm = (M % 256 == 0 || M > 1024) ? 256 : 128;
     if (bn == 0) bn = (bm == 256 && N >= 256) ? 256 : 128;
-    if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4>>(g, stream);
-    if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6>>(g, stream);
-    if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 6>>(g, stream);
-    return fail(S24_ERR_UNSUPPORTED, "spmm: no kernel for tile %d x %d (have 256x256, 256x128, 128x128)", bm, bn);
+    if (prune_out) {
+        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, true>>(g, stream);
+        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, true>>(g, stream);
+        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, true>>(g, stream);
+    } else {
+        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4>>(g, stream);
+        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6>>(g, stream);
+        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4>>(g, stream);
+    }
+    return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 256x256, 256x128, 128x128)", who, bm, bn);
 }
 
 }  // namespace s24
@@ -479,10 +572,12 @@ extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const v
     return run_spmm(vals, workspace, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int s24_spmm_prune_out(const void*, const void*, const void*, void*, void*, void*, int64_t, int64_t, int64_t,
-                                  int64_t, int, const s24_tile_cfg*, void*)
+extern "C" int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void* B, void* C_vals, void* C_meta_ref,
+                                  void* C_meta_tc, int64_t M, int64_t N, int64_t K, int64_t ldb, int dtype,
+                                  const s24_tile_cfg* cfg, void* stream)
 {
-    return fail(S24_ERR_UNSUPPORTED, "spmm_prune_out: not built yet");
+    return run_spmm(vals, meta_tc, B, nullptr, M, N, K, ldb, N, dtype, cfg, static_cast<cudaStream_t>(stream), true,
+                    C_vals, C_meta_ref, C_meta_tc);
 }
 
 extern "C" int s24_device_status(void* stream)

@@ -191,17 +191,23 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
     return c
 
 
-def spmm_prune_out(vals: torch.Tensor, meta_tc: torch.Tensor, B: torch.Tensor, want_ref: bool = True,
-                   want_tc: bool = False, manual_config: Optional[dict] = None):
+def spmm_prune_out(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: str = "tc",
+                   want_ref: bool = True, want_tc: bool = False, manual_config: Optional[dict] = None):
     """Sparse GEMM whose epilogue 2:4-prunes and compresses the accumulator along N
     (compression/kernels/10.1_prune_acc.py:88-154,624-678).
 
     Returns (C_vals (M, N/2), C_meta (M/16, N) int16 or None, C_meta_tc or None).
     """
-    _require_cuda(vals, meta_tc, B)
+    _require_cuda(vals, meta, B)
     M, N, K = _check_gemm(vals, B)
     if N % 128 != 0:
         raise RuntimeError(f"fused output prune needs N % 128 == 0 (got {N})")
+    if meta_layout == "ref":
+        meta_tc = meta_convert(meta, "ref", "tc", M, K)
+    elif meta_layout == "tc":
+        meta_tc = meta
+    else:
+        raise ValueError(f"unknown metadata layout {meta_layout!r}")
     v = vals.contiguous()
     b = _row_major(B)
     cv = torch.empty((M, N // 2), dtype=vals.dtype, device=vals.device)
