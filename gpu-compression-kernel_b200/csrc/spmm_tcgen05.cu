@@ -572,6 +572,52 @@ extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const v
     return run_spmm(vals, workspace, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------- scratch owned by the library
+//
+// Workspace for s24_spmm_ref_meta_noalloc: callers with a device-memory budget fixed at
+// start-up (or a loop that cannot afford cudaMalloc's synchronisation) have no buffer to lend
+// us, so the converted metadata lives in this array inside the library image.  In host code
+// the name g_static_scratch is only a handle for the runtime, not a device address: the
+// address kernels can use comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+static __device__ __align__(256) unsigned char g_static_scratch[S24_STATIC_SCRATCH_BYTES];
+
+static void* static_scratch_address()
+{
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev), "cudaGetDevice") != S24_OK) return nullptr;
+    if (dev < 0 || dev >= 64) {
+        fail(S24_ERR_UNSUPPORTED, "static scratch: device ordinal %d out of range", dev);
+        return nullptr;
+    }
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)") != S24_OK)
+            return nullptr;
+        cached[dev] = ptr;
+    }
+    return cached[dev];
+}
+
+extern "C" int s24_spmm_ref_meta_noalloc(const void* vals, const void* meta_ref, const void* B, void* C, int64_t M,
+                                         int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,
+                                         const s24_tile_cfg* cfg, void* stream)
+{
+    if (M <= 0 || K <= 0) return fail(S24_ERR_SHAPE, "spmm_ref_meta_noalloc: M and K must be positive");
+    const size_t need = s24_meta_tc_bytes(M, K);
+    if (need > (size_t)S24_STATIC_SCRATCH_BYTES)
+        return fail(S24_ERR_SHAPE,
+                    "spmm_ref_meta_noalloc: metadata of a %lld x %lld matrix needs %zu bytes of scratch but the "
+                    "library's built-in buffer holds %zu; use s24_spmm_ref_meta with your own workspace",
+                    (long long)M, (long long)K, need, (size_t)S24_STATIC_SCRATCH_BYTES);
+    void* scratch = static_scratch_address();   // first call per device: address lookup, no allocation
+    if (scratch == nullptr) return S24_ERR_CUDA;
+    int rc = s24_meta_convert(meta_ref, S24_META_REF, scratch, S24_META_TC, M, K, stream);
+    if (rc) return rc;
+    return run_spmm(vals, scratch, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void* B, void* C_vals, void* C_meta_ref,
                                   void* C_meta_tc, int64_t M, int64_t N, int64_t K, int64_t ldb, int dtype,
                                   const s24_tile_cfg* cfg, void* stream)

@@ -13,6 +13,7 @@ FP16, BF16 = 0, 1
 MODE_SIGNED, MODE_MAGNITUDE = 0, 1
 TIE_REFERENCE, TIE_LOWER, TIE_HIGHER = 0, 1, 2
 META_LOGICAL, META_REF, META_TC = 0, 1, 2
+STATIC_SCRATCH_BYTES = 8 << 20
 
 # every symbol include/s24.h declares, with (restype, argtypes)
 _vp, _i64, _i32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
@@ -33,6 +34,8 @@ SIGNATURES = {
     "s24_spmm": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, ctypes.POINTER(TileCfg), _vp]),
     "s24_spmm_ref_meta": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
                                  ctypes.POINTER(TileCfg), _vp, _sz, _vp]),
+    "s24_spmm_ref_meta_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
+                                         ctypes.POINTER(TileCfg), _vp]),
     "s24_spmm_prune_out": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32,
                                   ctypes.POINTER(TileCfg), _vp]),
     "s24_device_status": (_i32, [_vp]),

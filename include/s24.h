@@ -154,6 +154,36 @@ S24_API int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const void
                       const s24_tile_cfg* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * s24_spmm_ref_meta for callers that cannot hand the library a workspace.  This entry point
+ * has no counterpart in the reference (whose launcher allocates freely through torch).
+ *
+ * Who needs it: code that runs with a device-memory budget fixed at start-up and may not
+ * allocate afterwards -- a plugin inside a serving process whose HBM was carved up among
+ * models when it started, an embedding host whose allocator must not be bypassed, a
+ * latency-bound loop that cannot afford cudaMalloc's device-wide synchronisation.  Such a
+ * caller owns its inputs and outputs but has nowhere to get the scratch buffer from.
+ *
+ * What it does: the re-laid metadata goes into a buffer of S24_STATIC_SCRATCH_BYTES that is
+ * part of the library image on the device (every GPU that loads libs24 holds these bytes
+ * until the process exits).  No cudaMalloc, cudaFree or allocating library routine is
+ * called.  Limits and rules:
+ *   - M * K / 8 must not exceed S24_STATIC_SCRATCH_BYTES (M * K <= 2^26, e.g. 8192 x 8192);
+ *     larger problems are rejected with S24_ERR_SHAPE and a message naming both sizes;
+ *   - the first call on each device looks up the buffer's device address
+ *     (cudaGetSymbolAddress) and caches it; make that first call, with the device current,
+ *     before any stream capture you may use;
+ *   - all calls on a device share the one buffer, which keeps whatever the previous call
+ *     left in it.  Every byte the GEMM reads is rewritten by the call itself, so nothing
+ *     needs clearing, but two calls whose kernels overlap on the GPU (different streams
+ *     without an ordering between them) race on it: serialise them.
+ * Arguments and all other rules as s24_spmm_ref_meta.
+ */
+#define S24_STATIC_SCRATCH_BYTES (8u << 20)
+S24_API int s24_spmm_ref_meta_noalloc(const void* vals, const void* meta_ref, const void* B, void* C,
+                              int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,
+                              const s24_tile_cfg* cfg, void* stream);
+
+/*
  * Sparse GEMM whose epilogue 2:4-prunes the fp32 accumulator along N and stores it
  * compressed (compression/kernels/10.1_prune_acc.py:88-154,624-678): C_vals (M, N/2) in
  * the element type (rounded after selection, :241) and metadata of the (M, N) result in
