@@ -91,6 +91,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_b
                  : "memory");
 }
 
+// CTA-local arrive + expected byte count (no cluster-scope release: the bytes are delivered by
+// the async proxy, whose completion the barrier itself orders)
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;

@@ -29,6 +29,7 @@
 
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 namespace s24 {
 
@@ -39,7 +40,7 @@ __device__ int g_status_word = 0;  // first device-side failure since the last s
 constexpr int kBlockK = 128;        // logical K per pipeline stage
 constexpr int kRowsPerCta = 128;
 constexpr int kGroupM = 8;          // M-tiles per raster group (compression/common.py:155)
-constexpr int kThreads = 192;       // producer warp, MMA warp, 4 epilogue warps
+constexpr int kThreads = 320;       // producer warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr uint32_t kTmemCols = 512;
 
 template <int G, int BN, int STAGES, bool PRUNE_OUT = false>
@@ -67,6 +68,7 @@ struct GemmParams {
     int64_t ldc;
     int M, N, K;
     int bf16;
+    int dbg_skip;   // TEMP experiment: bit0 skip A loads, bit1 skip B, bit2 skip E
     int* status;
     // fused output prune (unused by the plain kernel)
     void* c_vals;
@@ -157,12 +159,12 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, G);
+            mbar_init(bar_full + 8 * s, 1);   // one arrive (the leader's producer) + both CTAs' bytes
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < ACC; ++a) {
             mbar_init(bar_acc_full + 8 * a, 1);
-            mbar_init(bar_acc_empty + 8 * a, 4 * G);
+            mbar_init(bar_acc_empty + 8 * a, 8 * G);   // every epilogue warp of every CTA
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -195,16 +197,21 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         break;
                     }
                     const uint32_t full = (G == 2) ? mapa(bar_full + 8 * s, full_owner) : (bar_full + 8 * s);
-                    mbar_arrive_expect_tx_cluster(full, (uint32_t)Cfg::kStageBytes);
+                    const bool ldA = !(p.dbg_skip & 1), ldB = !(p.dbg_skip & 2), ldE = !(p.dbg_skip & 4);
+                    // the leader announces the bytes of both CTAs; the peer's copies complete on the
+                    // leader's barrier too (its byte count may run ahead of the announcement, which
+                    // the transaction count tolerates)
+                    if (leader)
+                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * ((ldA ? Cfg::kABytes : 0) + (ldB ? Cfg::kBBytes : 0) + (ldE ? Cfg::kEBytes : 0))));
                     const uint32_t a_dst = smem_a + s * Cfg::kABytes;
                     const uint32_t b_dst = smem_b + s * Cfg::kBBytes;
                     const uint32_t e_dst = smem_e + s * Cfg::kEBytes;
                     if (G == 2) {
-                        tma_load_2d_pair(a_dst, &tm_a, kb * 64, row0, full);
+                        if (ldA) tma_load_2d_pair(a_dst, &tm_a, kb * 64, row0, full);
 #pragma unroll
                         for (int i = 0; i < Cfg::kBNCta / 64; ++i)
-                            tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                        tma_load_2d_pair(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
+                            if (ldB) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        if (ldE) tma_load_2d_pair(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
                     } else {
                         tma_load_2d(a_dst, &tm_a, kb * 64, row0, full);
 #pragma unroll
@@ -265,7 +272,9 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else {
         // ------------------------------------------------------------ epilogue warps
-        const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        const int quad = warp & 3;         // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+        const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
+        constexpr int CW = BN / 2;         // columns per epilogue warp
         int a = 0;
         uint32_t acc_phase = 0;
         const uint32_t acc_empty_leader = (G == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
@@ -277,19 +286,22 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 break;
             }
             tc_fence_after();
-            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN);
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * CW);
             const int64_t row = (int64_t)(tm * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
-            const int col0 = tn * BN;
+            const int col0 = tn * BN + half * CW;
             if constexpr (!Cfg::kPruneOut) {
-                uint32_t packed[BN / 2];
+                uint32_t packed[CW / 2];
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
+                for (int c = 0; c < CW / 32; c += 2) {
+                    uint32_t r0[32], r1[32];   // two loads in flight per wait
+                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r0);
+                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32 + 32), r1);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        packed[c * 16 + i] = pack2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), p.bf16);
+                    for (int i = 0; i < 16; ++i) {
+                        packed[c * 16 + i] = pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]), p.bf16);
+                        packed[c * 16 + 16 + i] = pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]), p.bf16);
+                    }
                 }
                 // accumulator is in registers: hand the TMEM stage back to the MMA warp
                 tc_fence_before();
@@ -299,7 +311,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (row < p.M) {
                     uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
 #pragma unroll
-                    for (int c8 = 0; c8 < BN / 8; ++c8) {
+                    for (int c8 = 0; c8 < CW / 8; ++c8) {
                         if (col0 + c8 * 8 < p.N)
                             *reinterpret_cast<uint4*>(crow + c8 * 8) =
                                 make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
@@ -307,10 +319,10 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
             } else {
                 // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
-                uint32_t vals[BN / 4];   // packed 16-bit pairs: 8 registers per 32 columns
-                uint32_t meta[BN / 32];  // codes of 8 groups, group g in bits 4g..4g+3
+                uint32_t vals[CW / 4];   // packed 16-bit pairs: 8 registers per 32 columns
+                uint32_t meta[CW / 32];  // codes of 8 groups, group g in bits 4g..4g+3
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < CW / 32; ++c) {
                     uint32_t r[32];
                     tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
                     tc_wait_ld();
@@ -333,7 +345,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (row_ok) {
                     uint16_t* vrow = static_cast<uint16_t*>(p.c_vals) + row * (int64_t)(p.N / 2) + col0 / 2;
 #pragma unroll
-                    for (int c = 0; c < BN / 32; ++c) {
+                    for (int c = 0; c < CW / 32; ++c) {
                         if (col0 + c * 32 < p.N) {
                             *reinterpret_cast<uint4*>(vrow + c * 16) =
                                 make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
@@ -349,7 +361,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const int m0 = lane & 7;
                 const int64_t row16 = row >> 4;
 #pragma unroll
-                for (int c2 = 0; c2 < BN / 64; ++c2) {
+                for (int c2 = 0; c2 < CW / 64; ++c2) {
                     const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2], 8);
                     const uint32_t xb = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2 + 1], 8);
                     uint32_t w0, w1;  // logical columns c and c+1 (16 columns each) of rows (r, r+8)
@@ -529,6 +541,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.N = (int)N;
     g.p.K = (int)K;
     g.p.bf16 = dtype == S24_BF16;
+    { const char* v = getenv("S24_DBG_SKIP"); g.p.dbg_skip = v ? atoi(v) : 0; }
     g.p.status = status;
     g.p.c_vals = c_vals;
     g.p.c_meta_ref = static_cast<uint32_t*>(c_meta_ref);
