@@ -245,35 +245,50 @@ S24_HD void keep_masks(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, uint3
     k3 = ge2<DT>(K3, second);
 }
 
-// scalar redo of one group (half = 0 low / 1 high of the packed registers): keep mask bits
-template <int DT, int MODE>
-S24_HD uint32_t scalar_keep(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, int half, int tie)
-{
-    const int sh = 16 * half;
-    const uint32_t e[4] = {(P0 >> sh) & 0xFFFFu, (P1 >> sh) & 0xFFFFu, (P2 >> sh) & 0xFFFFu, (P3 >> sh) & 0xFFFFu};
-    float k[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float v = bits_to_float(e[i], DT);
-        k[i] = (MODE == kModeMagnitude) ? (v < 0.f ? -v : v) : v;
-    }
-    return keep_mask_scalar(k, tie);
-}
+S24_HD uint32_t maj3(uint32_t a, uint32_t b, uint32_t c) { return (a & b) | (a & c) | (b & c); }
 
+// Groups with a tie across the keep/drop boundary (tiebits = 0xFFFF in their half): redo the keep
+// masks with pairwise comparisons under the requested tie rule, still two groups at a time and
+// without branches, and patch them in.  Element i "beats" j when it ranks ahead of it; an element
+// survives when it beats at least two others.
+//   kTieLower      i < j: i beats j on >=
+//   kTieHigher     i < j: i beats j on >  (the higher index wins equal keys)
+//   kTieReference  as kTieLower, except where element 0 is the strict minimum: then the smallest
+//                  of elements 1..3 is dropped, the lowest index among equals, and if all three
+//                  are equal elements 1 and 3 survive (keep_mask_scalar states the same rule and
+//                  is checked against the table measured from the reference)
 template <int DT, int MODE>
 S24_HD void fix_tied_masks(uint32_t P0, uint32_t P1, uint32_t P2, uint32_t P3, uint32_t tiebits, int tie, uint32_t& k0,
                            uint32_t& k1, uint32_t& k2, uint32_t& k3)
 {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const uint32_t hm = 0xFFFFu << (16 * half);
-        if ((tiebits & hm) == 0) continue;
-        const uint32_t m = scalar_keep<DT, MODE>(P0, P1, P2, P3, half, tie);
-        k0 = (k0 & ~hm) | ((m & 1u) ? hm : 0u);
-        k1 = (k1 & ~hm) | ((m & 2u) ? hm : 0u);
-        k2 = (k2 & ~hm) | ((m & 4u) ? hm : 0u);
-        k3 = (k3 & ~hm) | ((m & 8u) ? hm : 0u);
+    const uint32_t km = MODE == kModeMagnitude ? 0x7FFF7FFFu : 0xFFFFFFFFu;
+    const uint32_t K0 = P0 & km, K1 = P1 & km, K2 = P2 & km, K3 = P3 & km;
+    uint32_t b01, b02, b03, b12, b13, b23;
+    if (tie == kTieHigher) {
+        b01 = ~ge2<DT>(K1, K0); b02 = ~ge2<DT>(K2, K0); b03 = ~ge2<DT>(K3, K0);
+        b12 = ~ge2<DT>(K2, K1); b13 = ~ge2<DT>(K3, K1); b23 = ~ge2<DT>(K3, K2);
+    } else {
+        b01 = ge2<DT>(K0, K1); b02 = ge2<DT>(K0, K2); b03 = ge2<DT>(K0, K3);
+        b12 = ge2<DT>(K1, K2); b13 = ge2<DT>(K1, K3); b23 = ge2<DT>(K2, K3);
     }
+    uint32_t n0 = maj3(b01, b02, b03), n1 = maj3(~b01, b12, b13), n2 = maj3(~b02, ~b12, b23), n3 = maj3(~b03, ~b13, ~b23);
+    if (tie == kTieReference) {
+        const uint32_t r21 = ge2<DT>(K2, K1), r31 = ge2<DT>(K3, K1), r32 = ge2<DT>(K3, K2);
+        const uint32_t zero_min = ~(b01 | b02 | b03);          // a0 < a1, a2, a3
+        const uint32_t alleq = b12 & r21 & b23 & r32;          // a1 == a2 == a3
+        const uint32_t one_min = r21 & r31;                    // a1 <= a2 and a1 <= a3
+        const uint32_t d1 = one_min & ~alleq;
+        const uint32_t d2 = (~one_min & r32) | alleq;
+        const uint32_t d3 = ~one_min & ~r32;
+        n0 = n0 & ~zero_min;
+        n1 = sel(zero_min, ~d1, n1);
+        n2 = sel(zero_min, ~d2, n2);
+        n3 = sel(zero_min, ~d3, n3);
+    }
+    k0 = sel(tiebits, n0, k0);
+    k1 = sel(tiebits, n1, k1);
+    k2 = sel(tiebits, n2, k2);
+    k3 = sel(tiebits, n3, k3);
 }
 
 // Complete treatment of 8 consecutive elements (two groups) held as four registers in

@@ -29,7 +29,6 @@
 
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
-#include <stdlib.h>
 
 namespace s24 {
 
@@ -68,7 +67,6 @@ struct GemmParams {
     int64_t ldc;
     int M, N, K;
     int bf16;
-    int dbg_skip;   // TEMP experiment: bit0 skip A loads, bit1 skip B, bit2 skip E
     int* status;
     // fused output prune (unused by the plain kernel)
     void* c_vals;
@@ -197,21 +195,20 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         break;
                     }
                     const uint32_t full = (G == 2) ? mapa(bar_full + 8 * s, full_owner) : (bar_full + 8 * s);
-                    const bool ldA = !(p.dbg_skip & 1), ldB = !(p.dbg_skip & 2), ldE = !(p.dbg_skip & 4);
                     // the leader announces the bytes of both CTAs; the peer's copies complete on the
                     // leader's barrier too (its byte count may run ahead of the announcement, which
                     // the transaction count tolerates)
                     if (leader)
-                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * ((ldA ? Cfg::kABytes : 0) + (ldB ? Cfg::kBBytes : 0) + (ldE ? Cfg::kEBytes : 0))));
+                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * Cfg::kStageBytes));
                     const uint32_t a_dst = smem_a + s * Cfg::kABytes;
                     const uint32_t b_dst = smem_b + s * Cfg::kBBytes;
                     const uint32_t e_dst = smem_e + s * Cfg::kEBytes;
                     if (G == 2) {
-                        if (ldA) tma_load_2d_pair(a_dst, &tm_a, kb * 64, row0, full);
+                        tma_load_2d_pair(a_dst, &tm_a, kb * 64, row0, full);
 #pragma unroll
                         for (int i = 0; i < Cfg::kBNCta / 64; ++i)
-                            if (ldB) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                        if (ldE) tma_load_2d_pair(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
+                            tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        tma_load_2d_pair(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
                     } else {
                         tma_load_2d(a_dst, &tm_a, kb * 64, row0, full);
 #pragma unroll
@@ -541,7 +538,6 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.N = (int)N;
     g.p.K = (int)K;
     g.p.bf16 = dtype == S24_BF16;
-    { const char* v = getenv("S24_DBG_SKIP"); g.p.dbg_skip = v ? atoi(v) : 0; }
     g.p.status = status;
     g.p.c_vals = c_vals;
     g.p.c_meta_ref = static_cast<uint32_t*>(c_meta_ref);
