@@ -60,8 +60,13 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi sampling of SM clocks and throttle reasons around the timed region.
+
+    nvidia-smi is polled every 20 ms with timestamps; `mark()` records the host time at the
+    start and end of the timed region and the summary uses the samples that fall inside it
+    (the timed GEMM loop is tens of milliseconds long, so samples outside it would only show
+    the idle clock)."""
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -69,18 +74,23 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.tmp = None
+        self.marks = []
 
     def start(self):
         try:
             self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu)], stdout=self.tmp, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    def mark(self):
+        self.marks.append(time.time())
+
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "samples_in_timed_region": 0}
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -91,22 +101,34 @@ class ClockSampler:
         self.tmp.flush()
         rows = [r.split(",") for r in Path(self.tmp.name).read_text().splitlines() if r.strip()]
         os.unlink(self.tmp.name)
-        sm, mx, reasons = [], [], set()
+        t0, t1 = (self.marks[0], self.marks[-1]) if len(self.marks) >= 2 else (0.0, float("inf"))
+        sm_all, sm_in, pw_in, mx, reasons = [], [], [], [], set()
         for r in rows:
-            if len(r) < 9:
+            if len(r) < 10:
                 continue
             try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
+                ts = datetime.datetime.strptime(r[0].strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, cmax, pw = float(r[2]), float(r[3]), float(r[4])
             except ValueError:
                 continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                if v.strip().lower() == "active":
+            sm_all.append(clk)
+            mx.append(cmax)
+            inside = t0 - 0.01 <= ts <= t1 + 0.01
+            if inside:
+                sm_in.append(clk)
+                pw_in.append(pw)
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[6:10]):
+                if v.strip().lower() == "active" and (inside or not sm_in):
                     reasons.add(name)
-        if sm:
-            # under load = the upper half of the samples (idle samples before / after pull the median down)
-            out["sm_mhz"] = float(np.median(sm))
+        if sm_all:
+            use = sm_in if sm_in else sm_all
+            out["sm_mhz"] = float(np.median(use))
+            out["sm_min_mhz"] = float(min(use))
             out["sm_max_mhz"] = float(max(mx))
-            out["samples"] = len(sm)
+            out["samples"] = len(sm_all)
+            out["samples_in_timed_region"] = len(sm_in)
+            if pw_in:
+                out["power_w_max"] = float(max(pw_in))
         out["reasons"] = sorted(reasons)
         return out
 
@@ -236,7 +258,9 @@ def run_ours(args, rank, world, local):
         sampler.start()
         time.sleep(0.25)
     barrier()
+    sampler.mark()
     ms = time_steps(gemm_step, args.steps, stream)
+    sampler.mark()
     barrier()
     rc = _lib.lib().s24_device_status(None)
     if rc != 0:
@@ -387,8 +411,8 @@ def run_profile_target(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--profile-target", choices=["gemm", "prune_compress"], default=None,

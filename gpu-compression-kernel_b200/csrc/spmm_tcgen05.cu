@@ -42,23 +42,33 @@ constexpr int kGroupM = 8;          // M-tiles per raster group (compression/com
 constexpr int kThreads = 320;       // producer warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr uint32_t kTmemCols = 512;
 
-template <int G, int BN, int STAGES, bool PRUNE_OUT = false>
+// G = CTAs per tile engine (1 or a pair), BN = tile columns, MT = 128-row sub-tiles per CTA:
+// with MT = 2 a CTA pair owns 512 rows as two 256-row MMAs that share every B stage, which cuts
+// the bytes brought into each SM per flop by a quarter and deepens the ring in MMA time.
+template <int G, int BN, int STAGES, bool PRUNE_OUT = false, int MT = 1>
 struct GemmCfg {
     static constexpr bool kPruneOut = PRUNE_OUT;
     static constexpr int kG = G;
     static constexpr int kBN = BN;
+    static constexpr int kMT = MT;
     static constexpr int kStages = STAGES;
-    static constexpr int kBNCta = BN / G;                       // B columns loaded per CTA
-    static constexpr int kABytes = kRowsPerCta * 128;           // 128 rows x 64 values x 2 B
+    static constexpr int kTileRows = kRowsPerCta * G * MT;
+    static constexpr int kBNCta = BN / G;                       // B columns this CTA feeds to the MMA
+    static constexpr int kASubBytes = kRowsPerCta * 128;        // 128 rows x 64 values x 2 B
+    static constexpr int kABytes = MT * kASubBytes;
     static constexpr int kBAtomBytes = kBlockK * 128;           // 128 k-rows x 64 columns x 2 B
-    static constexpr int kBBytes = (kBNCta / 64) * kBAtomBytes;
-    static constexpr int kEBytes = 2048;
+    static constexpr int kBAtoms = (kBNCta + 63) / 64;          // loaded as whole 64-column atoms
+    static constexpr int kBBytes = kBAtoms * kBAtomBytes;
+    static constexpr int kESubBytes = 2048;
+    static constexpr int kEBytes = MT * kESubBytes;
     static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;
-    static constexpr int kAccStages = (BN == 256) ? 1 : 2;
-    static constexpr int kECol0 = kAccStages * BN;              // metadata columns follow the accumulators
+    static constexpr int kAccCols = BN * MT;                    // one accumulator set
+    static constexpr int kAccStages = (kAccCols >= 256) ? 1 : 2;
+    static constexpr int kECol0 = kAccStages * kAccCols;        // metadata columns follow the accumulators
     static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static_assert(kECol0 + 4 * STAGES <= (int)kTmemCols, "tensor memory budget");
-    static_assert(kBNCta % 64 == 0, "B is loaded in 64-column swizzle atoms");
+    static_assert(kECol0 + 4 * MT * STAGES <= (int)kTmemCols, "tensor memory budget");
+    static_assert(kBNCta % 8 == 0 && BN % (16 * G) == 0, "MMA N granularity");
+    static_assert(!PRUNE_OUT || (MT == 1 && BN % 128 == 0), "the pruning epilogue works on 64-column units");
     static_assert(kSmemBytes <= 232448, "shared memory budget (227 KB per CTA)");
 };
 
@@ -124,6 +134,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     constexpr int BN = Cfg::kBN;
     constexpr int STAGES = Cfg::kStages;
     constexpr int ACC = Cfg::kAccStages;
+    constexpr int MT = Cfg::kMT;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -148,7 +159,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t cta_rank = (G == 2) ? cluster_ctarank() : 0u;
     const bool leader = cta_rank == 0;
 
-    const int num_m = (p.M + kRowsPerCta * G - 1) / (kRowsPerCta * G);
+    const int num_m = (p.M + Cfg::kTileRows - 1) / Cfg::kTileRows;
     const int num_n = (p.N + BN - 1) / BN;
     const int num_tiles = num_m * num_n;
     const int num_units = (int)gridDim.x / G;
@@ -186,9 +197,9 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
                 int tm, tn;
                 tile_coords(t, num_m, num_n, tm, tn);
-                const int row0 = (tm * G + (int)cta_rank) * kRowsPerCta;
+                // sub-tile m of this CTA: rows row0 + m * 128 * G .. + 127
+                const int row0 = tm * Cfg::kTileRows + (int)cta_rank * kRowsPerCta;
                 const int col0 = tn * BN + (int)cta_rank * Cfg::kBNCta;
-                const int rec0 = (tm * G + (int)cta_rank) * kblocks;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u)) {
                         report_timeout(p.status, abort_flag, 1);
@@ -203,18 +214,22 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const uint32_t a_dst = smem_a + s * Cfg::kABytes;
                     const uint32_t b_dst = smem_b + s * Cfg::kBBytes;
                     const uint32_t e_dst = smem_e + s * Cfg::kEBytes;
-                    if (G == 2) {
-                        tma_load_2d_pair(a_dst, &tm_a, kb * 64, row0, full);
 #pragma unroll
-                        for (int i = 0; i < Cfg::kBNCta / 64; ++i)
-                            tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                        tma_load_2d_pair(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
-                    } else {
-                        tma_load_2d(a_dst, &tm_a, kb * 64, row0, full);
+                    for (int m = 0; m < MT; ++m) {
+                        const int rows = row0 + m * kRowsPerCta * G;
+                        const int rec = (rows / kRowsPerCta) * kblocks + kb;
+                        if (G == 2) {
+                            tma_load_2d_pair(a_dst + m * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
+                            tma_load_2d_pair(e_dst + m * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
+                        } else {
+                            tma_load_2d(a_dst + m * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
+                            tma_load_2d(e_dst + m * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
+                        }
+                    }
 #pragma unroll
-                        for (int i = 0; i < Cfg::kBNCta / 64; ++i)
-                            tma_load_2d(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                        tma_load_2d(e_dst, &tm_e, 0, (rec0 + kb) * 4, full);
+                    for (int i = 0; i < Cfg::kBAtoms; ++i) {
+                        if (G == 2) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        else tma_load_2d(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
                     }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
@@ -232,7 +247,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     break;
                 }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(a * Cfg::kAccCols);
                 bool ok = true;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(bar_full + 8 * s, phase)) {
@@ -241,9 +256,12 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t e_cols = tmem_base + (uint32_t)(Cfg::kECol0 + 4 * s);
-                    // metadata record: 128 rows of 16 bytes, 8-row core matrices 128 bytes apart
-                    tc_cp_128x128b<G>(e_cols, make_smem_desc(smem_e + s * Cfg::kEBytes, 128, 128, kSwizzleNone));
+                    const uint32_t e_cols = tmem_base + (uint32_t)(Cfg::kECol0 + 4 * MT * s);
+                    // metadata records: 128 rows of 16 bytes, 8-row core matrices 128 bytes apart
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                        tc_cp_128x128b<G>(e_cols + 4 * m,
+                                          make_smem_desc(smem_e + s * Cfg::kEBytes + m * Cfg::kESubBytes, 128, 128, kSwizzleNone));
                     // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
                     const uint64_t adesc = make_smem_desc(smem_a + s * Cfg::kABytes, 16, 1024, kSwizzle128B);
                     // B: N-major, 128-byte swizzle; 64-column atoms kBAtomBytes apart (leading),
@@ -252,10 +270,13 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // K = 32 per instruction: 32 bytes further along A's rows, 32 k-rows (4096 B) into B,
-                        // metadata column j (even column address + selector bit)
-                        tc_mma_sp_f16<G>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 256),
-                                         idesc | (uint32_t)(j & 1), e_cols + (uint32_t)(j & 2),
-                                         (kb | j) != 0 ? 1u : 0u);
+                        // metadata column j (even column address + selector bit); the sub-tiles reuse
+                        // the same B slice back to back
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+                            tc_mma_sp_f16<G>(tmem_d + (uint32_t)(m * BN), adesc + (uint64_t)(m * (Cfg::kASubBytes >> 4) + j * 2),
+                                             bdesc + (uint64_t)(j * 256), idesc | (uint32_t)(j & 1),
+                                             e_cols + (uint32_t)(4 * m + (j & 2)), (kb | j) != 0 ? 1u : 0u);
                     }
                     if (G == 2) tc_commit_pair(bar_empty + 8 * s, 3);
                     else tc_commit<1>(bar_empty + 8 * s);
@@ -270,8 +291,11 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     } else {
         // ------------------------------------------------------------ epilogue warps
         const int quad = warp & 3;         // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
-        const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
-        constexpr int CW = BN / 2;         // columns per epilogue warp
+        const int half = (warp - 2) >> 2;  // second epilogue warp of the quadrant
+        // MT == 1: the two warps of a quadrant split the tile's columns; MT == 2: each takes one sub-tile
+        constexpr int CW = (MT == 2) ? BN : BN / 2;   // columns per epilogue warp
+        const int sub = (MT == 2) ? half : 0;
+        const int chalf = (MT == 2) ? 0 : half;
         int a = 0;
         uint32_t acc_phase = 0;
         const uint32_t acc_empty_leader = (G == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
@@ -283,21 +307,26 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 break;
             }
             tc_fence_after();
-            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * BN + half * CW);
-            const int64_t row = (int64_t)(tm * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
-            const int col0 = tn * BN + half * CW;
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * Cfg::kAccCols + sub * BN + chalf * CW);
+            const int64_t row = (int64_t)tm * Cfg::kTileRows + (sub * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
+            const int col0 = tn * BN + chalf * CW;
             if constexpr (!Cfg::kPruneOut) {
                 uint32_t packed[CW / 2];
+                constexpr int NCH = CW / 32;               // 32-column chunks
+                constexpr bool kTwoLoads = CW <= 128;      // two loads in flight per wait when registers allow
 #pragma unroll
-                for (int c = 0; c < CW / 32; c += 2) {
-                    uint32_t r0[32], r1[32];   // two loads in flight per wait
+                for (int c = 0; c < NCH; c += (kTwoLoads ? 2 : 1)) {
+                    uint32_t r0[32], r1[32];
                     tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r0);
-                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32 + 32), r1);
+                    if (kTwoLoads && c + 1 < NCH) tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32 + 32), r1);
                     tc_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
+                    for (int i = 0; i < 16; ++i)
                         packed[c * 16 + i] = pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]), p.bf16);
-                        packed[c * 16 + 16 + i] = pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]), p.bf16);
+                    if (kTwoLoads && c + 1 < NCH) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            packed[c * 16 + 16 + i] = pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]), p.bf16);
                     }
                 }
                 // accumulator is in registers: hand the TMEM stage back to the MMA warp
@@ -465,7 +494,7 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
     rc = check_cuda(cudaFuncSetAttribute(spmm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
                     "cudaFuncSetAttribute(max dynamic shared memory)");
     if (rc) return rc;
-    const int num_m = (int)((g.M + kRowsPerCta * Cfg::kG - 1) / (kRowsPerCta * Cfg::kG));
+    const int num_m = (int)((g.M + Cfg::kTileRows - 1) / Cfg::kTileRows);
     const int num_n = (int)((g.N + Cfg::kBN - 1) / Cfg::kBN);
     const int tiles = num_m * num_n;
     int units = sm_count() / Cfg::kG;
@@ -544,18 +573,26 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.c_meta_tc = static_cast<uint32_t*>(c_meta_tc);
 
     int bm = cfg ? cfg->bm : 0, bn = cfg ? cfg->bn : 0;
+    // Heuristic (measured on B200): the 512x224 tile moves a quarter fewer bytes into each SM per
+    // flop and is the most energy-efficient variant, which is what counts once the part is power
+    // capped; it needs enough K to amortise its single-buffered accumulators and enough rows.
+    if (bm == 0 && bn == 0 && !prune_out && K >= 4096 && M >= 1024 && N >= 1024) {
+        bm = 512;
+        bn = 224;
+    }
     if (bm == 0) bm = (M % 256 == 0 || M > 1024) ? 256 : 128;
-    if (bn == 0) bn = (bm == 256 && N >= 256) ? 256 : 128;
+    if (bn == 0) bn = (bm == 512) ? 224 : ((bm == 256 && N >= 256) ? 256 : 128);
     if (prune_out) {
         if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, true>>(g, stream);
         if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, true>>(g, stream);
         if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, true>>(g, stream);
     } else {
+        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, false, 2>>(g, stream);
         if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4>>(g, stream);
         if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6>>(g, stream);
         if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4>>(g, stream);
     }
-    return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 256x256, 256x128, 128x128)", who, bm, bn);
+    return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 512x224 [plain GEMM only], 256x256, 256x128, 128x128)", who, bm, bn);
 }
 
 }  // namespace s24

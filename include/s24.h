@@ -80,8 +80,8 @@ extern "C" {
 /* Optional tile choice for the GEMM entry points; NULL or zeros = heuristic.
  * Mirrors the keys of the reference's manual_config (gluon_ws_sparse.py:629-636). */
 typedef struct s24_tile_cfg {
-    int bm;        /* rows per tile: 128 (one CTA) or 256 (CTA pair), 0 = auto */
-    int bn;        /* columns per tile: 128 or 256, 0 = auto */
+    int bm;        /* rows per tile: 128 (one CTA), 256 (CTA pair) or 512 (CTA pair, two row sub-tiles), 0 = auto */
+    int bn;        /* columns per tile: 128 or 256; 224 with bm = 512; 0 = auto */
     int stages;    /* depth of the shared-memory ring, 0 = auto */
     int reserved;
 } s24_tile_cfg;

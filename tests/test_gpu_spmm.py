@@ -45,7 +45,7 @@ def _check(C, ref32):
     torch.testing.assert_close(C.float(), ref32, rtol=RTOL, atol=ATOL + 4e-3 * float(ref32.abs().max()))
 
 
-@pytest.mark.parametrize("cfg", [{"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}])
+@pytest.mark.parametrize("cfg", [{"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
 def test_identity_b_reveals_decompressed_a(mods, cfg):
     """B = I makes C the dense 2:4 matrix itself, exactly: checks values, metadata layout
     and operand descriptors independently of any accumulation."""
@@ -61,7 +61,7 @@ def test_identity_b_reveals_decompressed_a(mods, cfg):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 256, 512), (384, 200, 384), (512, 1032, 1280), (1024, 768, 2048)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}])
+@pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
 def test_spmm_vs_fp32_reference(mods, M, N, K, dtype, cfg):
     s24 = mods["s24"]
     A, B, ap, vals, ml, e = _prepare(M, K, N, dtype, 100 + M + N + K)
