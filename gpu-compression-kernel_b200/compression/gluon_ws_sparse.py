@@ -31,9 +31,9 @@ def _normalise_config(manual_config):
         warnings.warn(f"ignoring unknown manual_config keys {sorted(unknown)}")
     cfg = {}
     bm, bn = manual_config.get("BM"), manual_config.get("BN")
-    if bm in (128, 256):
+    if bm in (128, 256, 512):
         cfg["BM"] = bm
-    if bn in (128, 256):
+    if bn in (128, 224, 256):
         cfg["BN"] = bn
     return cfg or None
 
@@ -41,8 +41,11 @@ def _normalise_config(manual_config):
 def run_sparse_ws_matmul(A, E, B, tune=True, manual_config=None):
     """C = A24 @ B (compression/gluon_ws_sparse.py:560-613); fp32 accumulate, C in A's dtype.
 
-    `tune=True` lets the library pick the tile (the reference autotunes over Triton
-    configs); with `tune=False` the BM / BN entries of `manual_config` are honoured.
+    `tune=True` times the library's tile shapes once per (M, N, K) and keeps the fastest (the
+    reference autotunes over its Triton configs the same way, :528-535,572-582); with
+    `tune=False` the BM / BN entries of `manual_config` are honoured, or the built-in
+    heuristic if there are none.
     """
-    cfg = None if tune else _normalise_config(manual_config)
-    return s24.spmm(A, E, B, meta_layout="ref", manual_config=cfg)
+    if tune:
+        return s24.spmm(A, E, B, meta_layout="ref", autotune=True)
+    return s24.spmm(A, E, B, meta_layout="ref", manual_config=_normalise_config(manual_config))

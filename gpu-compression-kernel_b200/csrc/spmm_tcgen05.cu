@@ -573,12 +573,27 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.c_meta_tc = static_cast<uint32_t*>(c_meta_tc);
 
     int bm = cfg ? cfg->bm : 0, bn = cfg ? cfg->bn : 0;
-    // Heuristic (measured on B200): the 512x224 tile moves a quarter fewer bytes into each SM per
-    // flop and is the most energy-efficient variant, which is what counts once the part is power
-    // capped; it needs enough K to amortise its single-buffered accumulators and enough rows.
-    if (bm == 0 && bn == 0 && !prune_out && K >= 4096 && M >= 1024 && N >= 1024) {
-        bm = 512;
-        bn = 224;
+    // Heuristic when the caller names no tile: score = (useful fraction of the persistent waves)
+    // x (relative throughput of the tile shape measured at large sizes on B200).  The 512x224
+    // tile moves a quarter fewer bytes into each SM per flop and is the most energy-efficient
+    // variant, which is what counts once the part is power capped; the smaller tiles win only
+    // when they fill the last wave better.
+    if (bm == 0 && bn == 0) {
+        struct Cand { int bm, bn, g; double eff; bool plain_only; };
+        const Cand cands[4] = {{512, 224, 2, 1.00, true}, {256, 256, 2, 0.97, false}, {256, 128, 2, 0.78, false},
+                               {128, 128, 1, 0.55, false}};
+        double best = -1.0;
+        for (const Cand& c : cands) {
+            if (c.plain_only && prune_out) continue;
+            if (c.bn > N + 127) continue;
+            const double useful = ((double)M / c.bm) * ((double)N / c.bn);
+            const int64_t tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
+            const int64_t units = sm_count() / c.g;
+            const int64_t waves = (tiles + units - 1) / units;
+            const double slots = (double)waves * (double)(tiles < units ? tiles : units);
+            const double score = useful / slots * c.eff;
+            if (score > best) { best = score; bm = c.bm; bn = c.bn; }
+        }
     }
     if (bm == 0) bm = (M % 256 == 0 || M > 1024) ? 256 : 128;
     if (bn == 0) bn = (bm == 512) ? 224 : ((bm == 256 && N >= 256) ? 256 : 128);

@@ -160,9 +160,44 @@ def _check_gemm(vals: torch.Tensor, B: torch.Tensor) -> Tuple[int, int, int]:
     return M, N, K
 
 
+_TILE_CANDIDATES = ({"BM": 512, "BN": 224}, {"BM": 256, "BN": 256}, {"BM": 256, "BN": 128}, {"BM": 128, "BN": 128})
+_TUNED = {}   # (M, N, K, dtype, device index) -> tile config chosen by timing
+
+
+def _autotune(vals, meta_tc, b, c, M, N, K):
+    """Time every tile shape once for this problem (CUDA events, 3 launches after a warm-up) and
+    remember the fastest, like the reference's Triton autotuner keyed on (M, N, K)
+    (compression/gluon_ws_sparse.py:528-535).  Synchronises, so it is skipped during stream capture."""
+    key = (M, N, K, vals.dtype, vals.device.index)
+    if key in _TUNED:
+        return _TUNED[key]
+    if torch.cuda.is_current_stream_capturing():
+        return None
+    stream = torch.cuda.current_stream(vals.device)
+    best, best_ms = None, float("inf")
+    for cfg in _TILE_CANDIDATES:
+        tc = _tile_cfg(cfg)
+
+        def launch():
+            L.check(L.lib().s24_spmm(_p(vals), _p(meta_tc), _p(b), _p(c), M, N, K, b.stride(0), c.stride(0),
+                                     _DT[vals.dtype], tc, _stream(vals)))
+        launch()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(3):
+            launch()
+        e1.record(stream)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1)
+        if ms < best_ms:
+            best, best_ms = cfg, ms
+    _TUNED[key] = best
+    return best
+
+
 def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: str = "tc",
          manual_config: Optional[dict] = None, out: Optional[torch.Tensor] = None,
-         workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+         workspace: Optional[torch.Tensor] = None, autotune: bool = False) -> torch.Tensor:
     """C = A24 @ B with fp32 accumulation (compression/gluon_ws_sparse.py:560-613).
 
     meta_layout "tc": `meta` is the tensor-core layout.  "ref": `meta` is the reference's
@@ -173,8 +208,16 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
     v = vals.contiguous()
     b = _row_major(B)
     c = out if out is not None else torch.empty((M, N), dtype=vals.dtype, device=vals.device)
-    cfg = _tile_cfg(manual_config)
     with torch.cuda.device(vals.device):
+        if meta_layout == "ref" and autotune and manual_config is None:
+            # tune on the converted metadata, then run through the native-layout entry point
+            if meta.numel() != M * K // 16:
+                raise RuntimeError(f"E has {meta.numel()} elements, expected {M * K // 16} for ({M}, {K})")
+            meta = meta_convert(meta, "ref", "tc", M, K)
+            meta_layout = "tc"
+        if autotune and manual_config is None and meta_layout == "tc":
+            manual_config = _autotune(v, meta, b, c, M, N, K)
+        cfg = _tile_cfg(manual_config)
         if meta_layout == "tc":
             L.check(L.lib().s24_spmm(_p(v), _p(meta), _p(b), _p(c), M, N, K, b.stride(0), c.stride(0),
                                      _DT[vals.dtype], cfg, _stream(vals)))
