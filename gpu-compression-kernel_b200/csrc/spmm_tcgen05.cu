@@ -311,57 +311,84 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const int64_t row = (int64_t)tm * Cfg::kTileRows + (sub * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
             const int col0 = tn * BN + chalf * CW;
             if constexpr (!Cfg::kPruneOut) {
-                uint32_t packed[CW / 2];
-                constexpr int NCH = CW / 32;               // 32-column chunks
-                constexpr bool kTwoLoads = CW <= 128;      // two loads in flight per wait when registers allow
+                // Drain in as few round trips as possible: one tcgen05.ld per 128 (then 64, then 32)
+                // columns, convert, and hand each 8-column group to the store unit right away, so
+                // only the load round trips (not the stores) stand between the MMA warp and its
+                // accumulator.
+                uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
+                const bool row_ok = row < p.M;
+                // 16 columns = 32 bytes = one full L2 sector per store when C allows it
+                const bool wide = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * 2)) & 31u) == 0;
+                auto emit = [&](const uint32_t* r, int c_off, int width) {
 #pragma unroll
-                for (int c = 0; c < NCH; c += (kTwoLoads ? 2 : 1)) {
-                    uint32_t r0[32], r1[32];
-                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r0);
-                    if (kTwoLoads && c + 1 < NCH) tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32 + 32), r1);
-                    tc_wait_ld();
+                    for (int i = 0; i < width / 16; ++i) {
+                        uint32_t q[8];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        packed[c * 16 + i] = pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]), p.bf16);
-                    if (kTwoLoads && c + 1 < NCH) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            packed[c * 16 + 16 + i] = pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]), p.bf16);
+                        for (int j = 0; j < 8; ++j)
+                            q[j] = pack2(__uint_as_float(r[16 * i + 2 * j]), __uint_as_float(r[16 * i + 2 * j + 1]), p.bf16);
+                        const int c = c_off + 16 * i;
+                        if (!row_ok) continue;
+                        if (wide && col0 + c + 16 <= p.N) {
+                            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(crow + c), "r"(q[0]), "r"(q[1]),
+                                         "r"(q[2]), "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7])
+                                         : "memory");
+                        } else {
+                            if (col0 + c < p.N) *reinterpret_cast<uint4*>(crow + c) = make_uint4(q[0], q[1], q[2], q[3]);
+                            if (col0 + c + 8 < p.N) *reinterpret_cast<uint4*>(crow + c + 8) = make_uint4(q[4], q[5], q[6], q[7]);
+                        }
                     }
+                };
+                int done = 0;
+#pragma unroll
+                for (int k = 0; k < CW / 128; ++k) {
+                    uint32_t r[128];
+                    tc_ld_32x32b_x128(tacc + (uint32_t)done, r);
+                    tc_wait_ld();
+                    emit(r, done, 128);
+                    done += 128;
                 }
-                // accumulator is in registers: hand the TMEM stage back to the MMA warp
+                if constexpr ((CW % 128) >= 64) {
+                    uint32_t r[64];
+                    tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
+                    tc_wait_ld();
+                    emit(r, done, 64);
+                    done += 64;
+                }
+                if constexpr ((CW % 64) >= 32) {
+                    uint32_t r[32];
+                    tc_ld_32x32b_x32(tacc + (uint32_t)done, r);
+                    tc_wait_ld();
+                    emit(r, done, 32);
+                    done += 32;
+                }
+                static_assert(CW % 32 == 0, "epilogue works in 32-column pieces");
+                // every accumulator column of this warp has been read: hand TMEM back to the MMA warp
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
-
-                if (row < p.M) {
-                    uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
-#pragma unroll
-                    for (int c8 = 0; c8 < CW / 8; ++c8) {
-                        if (col0 + c8 * 8 < p.N)
-                            *reinterpret_cast<uint4*>(crow + c8 * 8) =
-                                make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
-                    }
-                }
             } else {
                 // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
                 uint32_t vals[CW / 4];   // packed 16-bit pairs: 8 registers per 32 columns
                 uint32_t meta[CW / 32];  // codes of 8 groups, group g in bits 4g..4g+3
 #pragma unroll
-                for (int c = 0; c < CW / 32; ++c) {
-                    uint32_t r[32];
-                    tc_ld_32x32b_x32(tacc + (uint32_t)(c * 32), r);
+                for (int c2 = 0; c2 < CW / 64; ++c2) {
+                    uint32_t r[64];   // one load round trip per 64 columns (the metadata unit)
+                    tc_ld_32x32b_x64(tacc + (uint32_t)(c2 * 64), r);
                     tc_wait_ld();
-                    uint32_t m = 0;
 #pragma unroll
-                    for (int g4 = 0; g4 < 8; ++g4) {
-                        float v0, v1;
-                        const uint32_t code = prune_group_f32(__uint_as_float(r[4 * g4]), __uint_as_float(r[4 * g4 + 1]),
-                                                              __uint_as_float(r[4 * g4 + 2]), __uint_as_float(r[4 * g4 + 3]), v0, v1);
-                        vals[c * 8 + g4] = pack2(v0, v1, p.bf16);   // rounded after selection (10.1_prune_acc.py:241)
-                        m |= code << (4 * g4);
+                    for (int h = 0; h < 2; ++h) {
+                        const int c = 2 * c2 + h;
+                        uint32_t m = 0;
+#pragma unroll
+                        for (int g4 = 0; g4 < 8; ++g4) {
+                            float v0, v1;
+                            const uint32_t code = prune_group_f32(__uint_as_float(r[32 * h + 4 * g4]), __uint_as_float(r[32 * h + 4 * g4 + 1]),
+                                                                  __uint_as_float(r[32 * h + 4 * g4 + 2]), __uint_as_float(r[32 * h + 4 * g4 + 3]), v0, v1);
+                            vals[c * 8 + g4] = pack2(v0, v1, p.bf16);   // rounded after selection (10.1_prune_acc.py:241)
+                            m |= code << (4 * g4);
+                        }
+                        meta[c] = m;
                     }
-                    meta[c] = m;
                 }
                 tc_fence_before();
                 __syncwarp();
