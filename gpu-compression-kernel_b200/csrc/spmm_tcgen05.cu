@@ -17,11 +17,16 @@
 //     record into 4 TMEM columns, then four tcgen05.mma.sp (K = 32 each) accumulate into
 //     TMEM; tcgen05.commit releases the stage and, after the last k-block, publishes the
 //     accumulator;
-//   * warps 2-5: epilogue.  tcgen05.ld the accumulator (each warp its own 32-lane
-//     quadrant, one row per thread), release TMEM, convert and store;
+//   * warps 2-9: epilogue, two warps per 32-lane TMEM quadrant (they split the tile's columns,
+//     or take one row sub-tile each).  One accumulator row per thread: wide tcgen05.ld
+//     (128 / 64 / 32 columns per round trip), convert, 32-byte stores issued as the data
+//     arrives, then TMEM is handed back to the MMA warp;
 //   * CTA pairs (cta_group::2): each CTA loads its own 128 rows of A and half of the B
 //     tile (no multicast), the leader CTA issues 256-row MMAs that read both CTAs' shared
-//     memory, completion is multicast to both CTAs' barriers.
+//     memory, completion is multicast to both CTAs' barriers.  Only the leader's producer
+//     arrives on the "full" barrier (with the byte count of both CTAs); the peer's copies
+//     complete on that barrier without an arrive of their own;
+//   * optionally (MT = 2) a pair owns two 256-row sub-tiles that share every B stage.
 // Every barrier wait is bounded; on a timeout the kernel records a code in the status word
 // (see s24_device_status), frees its tensor memory and returns.
 #include "s24_common.cuh"
