@@ -523,9 +523,19 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
                      CU_TENSOR_MAP_SWIZZLE_NONE, "metadata");
     if (rc) return rc;
 
-    rc = check_cuda(cudaFuncSetAttribute(spmm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
-                    "cudaFuncSetAttribute(max dynamic shared memory)");
-    if (rc) return rc;
+    {
+        // opt in to the large dynamic shared-memory size once per device and kernel variant
+        static bool opted_in[64] = {false};
+        int dev = 0;
+        rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+        if (rc) return rc;
+        if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+            rc = check_cuda(cudaFuncSetAttribute(spmm_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes),
+                            "cudaFuncSetAttribute(max dynamic shared memory)");
+            if (rc) return rc;
+            if (dev >= 0 && dev < 64) opted_in[dev] = true;
+        }
+    }
     const int num_m = (int)((g.M + Cfg::kTileRows - 1) / Cfg::kTileRows);
     const int num_n = (int)((g.N + Cfg::kBN - 1) / Cfg::kBN);
     const int tiles = num_m * num_n;

@@ -64,6 +64,9 @@ def main():
     ap.add_argument("--quick", action="store_true", help="4 x 4 grid instead of 13 x 13")
     ap.add_argument("--out", default="-")
     ap.add_argument("--skip-done", action="store_true")
+    ap.add_argument("--vendor", action="store_true",
+                    help="also time torch's semi-structured sparse matmul (cuSPARSELt / CUTLASS behind "
+                         "torch.sparse.to_sparse_semi_structured), the stand-in for the reference's torchao line")
     ap.add_argument("--max-elems", type=float, default=2.5e9, help="skip shapes whose M*K exceeds this")
     args = ap.parse_args()
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
@@ -114,6 +117,19 @@ def main():
             s24.spmm(v, t, B, out=C)
 
         rec["two_kernel"] = tf(timeit(two_kernel))
+        if args.vendor:
+            try:
+                from torch.sparse import to_sparse_semi_structured
+                A_sp = to_sparse_semi_structured(A_pruned)
+                rec["vendor_sparse"] = tf(timeit(lambda: torch.mm(A_sp, B)))
+
+                def vendor_e2e():
+                    torch.mm(to_sparse_semi_structured(s24.prune(A)), B)
+
+                rec["vendor_two_step"] = tf(timeit(vendor_e2e))
+                del A_sp
+            except Exception as exc:  # library missing or shape unsupported on this box
+                rec["vendor_error"] = f"{type(exc).__name__}: {exc}"[:200]
         if N % 128 == 0:
             rec["fused_out"] = tf(timeit(lambda: s24.spmm_prune_out(vals, tc, B)))
 

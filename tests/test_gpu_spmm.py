@@ -150,3 +150,58 @@ def test_linearity_at_full_size(mods):
     rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8191], device=DEV)
     ref = Ap[rows].float() @ B1.float()
     torch.testing.assert_close(C1[rows].float(), ref.to(torch.float16).float(), rtol=RTOL, atol=ATOL)
+
+
+def test_strided_b_and_strided_output_through_the_c_abi(mods):
+    """row strides larger than the logical widths: B a column slice of a wider matrix, C written
+    into a column slice of a wider buffer (ldb, ldc > N), as the multi-GPU wrapper could do"""
+    import ctypes
+    from s24 import _lib
+    s24 = mods["s24"]
+    M, K, N = 256, 512, 328                       # N % 8 == 0 but not a multiple of 16
+    A, _, ap, vals, ml, e = _prepare(M, K, 1024, torch.float16, 555)
+    Bwide = randn((K, 1024), torch.float16, 556).to(DEV)
+    Bv = Bwide[:, 64:64 + N]                      # ldb = 1024, 16-byte aligned start
+    Cwide = torch.zeros(M, 640, dtype=torch.float16, device=DEV)
+    Cv = Cwide[:, 32:32 + N]                      # ldc = 640
+    tc = torch.from_numpy(oracle.meta_tc(ml, K).view(np.int32)).to(DEV)
+    v = from_bits(vals, torch.float16, DEV)
+    for cfg in (None, _lib.TileCfg(512, 224, 0, 0), _lib.TileCfg(128, 128, 0, 0)):
+        Cwide.zero_()
+        rc = _lib.lib().s24_spmm(ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(tc.data_ptr()),
+                                 ctypes.c_void_p(Bv.data_ptr()), ctypes.c_void_p(Cv.data_ptr()), M, N, K, 1024, 640,
+                                 _lib.FP16, ctypes.byref(cfg) if cfg is not None else None, None)
+        assert rc == 0, _lib.last_error()
+        _status_ok(s24)
+        ref = from_bits(ap, torch.float16, DEV).float() @ Bv.float()
+        _check(Cv, ref)
+        assert float(Cwide[:, :32].abs().max()) == 0 and float(Cwide[:, 32 + N:].abs().max()) == 0   # nothing outside the slice
+
+
+def test_launchers_can_be_captured_in_a_cuda_graph(mods):
+    """the reference's benchmarks run every launcher under CUDA-graph capture
+    (triton do_bench_cudagraph, dev/8.11_benchmark_2_kernel.py:52-61): capture the two-kernel path
+    and the reference-layout launcher, replay, compare with the eager result"""
+    s24 = mods["s24"]
+    M, K, N = 512, 1024, 1024
+    A = randn((M, K), torch.float16, 801).to(DEV)
+    B = randn((K, N), torch.float16, 802).to(DEV)
+    vals, E, tc = s24.prune_compress(A, want_ref=True, want_tc=True)
+    eager = s24.spmm(vals, tc, B)
+    eager2 = mods["two"].run_2_kernel_ws_matmul(A, B, tie="reference")
+    assert torch.equal(eager, eager2)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            c1 = mods["two"].run_2_kernel_ws_matmul(A, B, tie="reference")
+            c2 = mods["ws"].run_sparse_ws_matmul(vals, E, B, tune=False)
+    torch.cuda.current_stream().wait_stream(side)
+    c1.zero_()
+    c2.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    _status_ok(s24)
+    assert torch.equal(c1, eager) and torch.equal(c2, eager)
