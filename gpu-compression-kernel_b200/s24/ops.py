@@ -24,6 +24,27 @@ def _stream(t: torch.Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
+class _on_device:
+    """`with _on_device(t):` makes t's device current for the library call; a no-op (and much
+    cheaper than torch.cuda.device) when it already is, which is the common case"""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, t: torch.Tensor):
+        self.idx = t.device.index
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _require_cuda(*ts: torch.Tensor) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -56,7 +77,7 @@ def prune(t: torch.Tensor, mode: str = "signed", tie: str = "reference") -> torc
     dt = _dtype_code(t)
     src = t.contiguous()
     out = torch.empty_like(src)
-    with torch.cuda.device(t.device):
+    with _on_device(t):
         L.check(L.lib().s24_prune(_p(src), _p(out), src.numel(), dt, _MODE[mode], _TIE[tie], _stream(t)))
     return out.view(t.shape)
 
@@ -93,7 +114,7 @@ def compress(dense: torch.Tensor, want_ref: bool = True, want_tc: bool = False):
     e = torch.empty((m // 16, k), dtype=torch.int16, device=dense.device) if want_ref else None
     tc = torch.empty((meta_tc_numel(m, k),), dtype=torch.int32, device=dense.device) if want_tc else None
     if m * k:
-        with torch.cuda.device(dense.device):
+        with _on_device(dense):
             L.check(L.lib().s24_compress(_p(d), m, k, d.stride(0), _DT[dense.dtype], _p(vals), _p(e), _p(tc),
                                          _stream(dense)))
     return vals, e, tc
@@ -112,7 +133,7 @@ def prune_compress(A: torch.Tensor, mode: str = "signed", tie: str = "reference"
     e = torch.empty((m // 16, k), dtype=torch.int16, device=A.device) if want_ref else None
     tc = torch.empty((meta_tc_numel(m, k),), dtype=torch.int32, device=A.device) if want_tc else None
     if m * k:
-        with torch.cuda.device(A.device):
+        with _on_device(A):
             L.check(L.lib().s24_prune_compress(_p(a), m, k, a.stride(0), _DT[A.dtype], _MODE[mode], _TIE[tie],
                                                _p(vals), _p(e), _p(tc), _stream(A)))
     return vals, e, tc
@@ -131,7 +152,7 @@ def meta_convert(src: torch.Tensor, from_layout: str, to_layout: str, M: int, K:
         dst = torch.empty((M // 16, K), dtype=torch.int16, device=src.device)
     else:
         dst = torch.empty((M, K // 16), dtype=torch.int16, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on_device(src):
         L.check(L.lib().s24_meta_convert(_p(src), _LAYOUT[from_layout], _p(dst), _LAYOUT[to_layout], M, K,
                                          _stream(src)))
     return dst
@@ -208,7 +229,7 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
     v = vals.contiguous()
     b = _row_major(B)
     c = out if out is not None else torch.empty((M, N), dtype=vals.dtype, device=vals.device)
-    with torch.cuda.device(vals.device):
+    with _on_device(vals):
         if meta_layout == "ref" and autotune and manual_config is None:
             # tune on the converted metadata, then run through the native-layout entry point
             if meta.numel() != M * K // 16:
@@ -256,7 +277,7 @@ def spmm_prune_out(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta
     cv = torch.empty((M, N // 2), dtype=vals.dtype, device=vals.device)
     ce = torch.empty((M // 16, N), dtype=torch.int16, device=vals.device) if want_ref else None
     ct = torch.empty((meta_tc_numel(M, N),), dtype=torch.int32, device=vals.device) if want_tc else None
-    with torch.cuda.device(vals.device):
+    with _on_device(vals):
         L.check(L.lib().s24_spmm_prune_out(_p(v), _p(meta_tc), _p(b), _p(cv), _p(ce), _p(ct), M, N, K,
                                            b.stride(0), _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
     return cv, ce, ct

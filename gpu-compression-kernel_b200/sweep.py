@@ -38,7 +38,13 @@ GRID = [768, 1024, 1536, 2048, 3072, 4096, 6144, 8192, 12288, 16384, 24576, 3276
 QUICK = [2048, 4096, 8192, 16384]
 
 
+USE_GRAPH = True
+
+
 def timeit(fn, target_ms=30.0):
+    """ms per call.  Like the reference's triton.testing.do_bench_cudagraph
+    (dev/8.11_benchmark_2_kernel.py:52-61) the calls are captured into one CUDA graph and the
+    replay is timed, so host-side launch cost does not count; --eager times plain launches."""
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
@@ -49,6 +55,23 @@ def timeit(fn, target_ms=30.0):
     b.synchronize()
     one = max(a.elapsed_time(b), 1e-3)
     n = int(max(3, min(200, target_ms / one)))
+    if USE_GRAPH:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(n):
+                    fn()
+            g.replay()
+            torch.cuda.synchronize()
+            a.record()
+            g.replay()
+            b.record()
+            b.synchronize()
+            ms = a.elapsed_time(b) / n
+            del g
+            return ms
+        except Exception:
+            torch.cuda.synchronize()
     a.record()
     for _ in range(n):
         fn()
@@ -64,11 +87,14 @@ def main():
     ap.add_argument("--quick", action="store_true", help="4 x 4 grid instead of 13 x 13")
     ap.add_argument("--out", default="-")
     ap.add_argument("--skip-done", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="time plain launches instead of CUDA-graph replays")
     ap.add_argument("--vendor", action="store_true",
                     help="also time torch's semi-structured sparse matmul (cuSPARSELt / CUTLASS behind "
                          "torch.sparse.to_sparse_semi_structured), the stand-in for the reference's torchao line")
     ap.add_argument("--max-elems", type=float, default=2.5e9, help="skip shapes whose M*K exceeds this")
     args = ap.parse_args()
+    global USE_GRAPH
+    USE_GRAPH = not args.eager
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     dev = torch.device("cuda", 0)
     N = args.n
