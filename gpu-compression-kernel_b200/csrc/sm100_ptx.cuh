@@ -73,22 +73,10 @@ __device__ __forceinline__ void fence_barrier_init()
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-__device__ __forceinline__ void fence_proxy_async()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 // arrive on a barrier given by its shared::cluster address (own CTA or a peer)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar),
-                 "r"(bytes)
-                 : "memory");
 }
 
 // CTA-local arrive + expected byte count (no cluster-scope release: the bytes are delivered by
@@ -143,12 +131,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
         "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
         : "memory");
-}
-
-// bring a tile into L2 only (no shared-memory destination, no completion to wait for)
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y)
-{
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 
 // ---------------------------------------------------------------- tensor memory

@@ -196,7 +196,6 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            const uint32_t full_owner = (G == 2) ? 0u : cta_rank;  // the leader's barriers collect both CTAs' bytes
             int s = 0;
             uint32_t phase = 0;
             for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
@@ -210,7 +209,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         report_timeout(p.status, abort_flag, 1);
                         break;
                     }
-                    const uint32_t full = (G == 2) ? mapa(bar_full + 8 * s, full_owner) : (bar_full + 8 * s);
+                    const uint32_t full = (G == 2) ? mapa(bar_full + 8 * s, 0) : (bar_full + 8 * s);   // the leader's barrier
                     // the leader announces the bytes of both CTAs; the peer's copies complete on the
                     // leader's barrier too (its byte count may run ahead of the announcement, which
                     // the transaction count tolerates)
