@@ -307,7 +307,7 @@ def run_ours(args, rank, world, local):
             stream.wait_event(ev_in[b])
             if i >= NBUF:
                 stream.wait_event(ev_down[b])                # the previous result in this slot has left
-            d_out[b] = gluon_ws_sparse.run_sparse_ws_matmul(*d_in[b])
+            d_out[b] = gluon_ws_sparse.run_sparse_ws_matmul(*d_in[b], tune=False)   # tile by the library's heuristic
             ev_free[b].record(stream)
             ev_done[b].record(stream)
             with torch.cuda.stream(s_out):
