@@ -14,7 +14,7 @@ import s24  # noqa: E402
 def _tiles(cfg):
     if not cfg:
         return None
-    return {k: cfg[k] for k in ("BM", "BN") if cfg.get(k) in (128, 256)} or None
+    return {k: cfg[k] for k in ("BM", "BN") if cfg.get(k) in (128, 224, 256, 512)} or None
 
 
 def run_matmul_then_compress_separate(A_comp, E_A, B, tune=True, manual_matmul_config=None,

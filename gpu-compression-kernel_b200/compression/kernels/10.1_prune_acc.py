@@ -20,7 +20,7 @@ def run_sparse_ws_matmul(A, E, B, tune=True, manual_config=None):
     survivors rounded afterwards (:241)."""
     cfg = None
     if not tune and manual_config:
-        cfg = {k: manual_config[k] for k in ("BM", "BN") if manual_config.get(k) in (128, 256)} or None
+        cfg = {k: manual_config[k] for k in ("BM", "BN") if manual_config.get(k) in (128, 224, 256, 512)} or None
     c_vals, c_meta, _ = s24.spmm_prune_out(A, E, B, meta_layout="ref", want_ref=True, want_tc=False, manual_config=cfg)
     return c_vals, c_meta
 

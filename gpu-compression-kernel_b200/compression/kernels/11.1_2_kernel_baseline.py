@@ -24,7 +24,7 @@ def run_2_kernel_ws_matmul(A, B, tune=True, manual_config=None, mode="signed", t
     vals, _, meta_tc = s24.prune_compress(A, mode=mode, tie=tie, want_ref=False, want_tc=True)
     cfg = None
     if not tune and manual_config:
-        cfg = {k: manual_config[k] for k in ("BM", "BN") if manual_config.get(k) in (128, 256)} or None
+        cfg = {k: manual_config[k] for k in ("BM", "BN") if manual_config.get(k) in (128, 224, 256, 512)} or None
     return s24.spmm(vals, meta_tc, B, meta_layout="tc", manual_config=cfg)
 
 

@@ -73,7 +73,7 @@ struct GemmCfg {
     static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static_assert(kECol0 + 4 * MT * STAGES <= (int)kTmemCols, "tensor memory budget");
     static_assert(kBNCta % 8 == 0 && BN % (16 * G) == 0, "MMA N granularity");
-    static_assert(!PRUNE_OUT || (MT == 1 && BN % 128 == 0), "the pruning epilogue works on 64-column units");
+    static_assert(BN % 32 == 0 && (BN / (MT == 2 ? 1 : 2)) % 32 == 0, "the epilogues work in 32-column chunks");
     static_assert(kSmemBytes <= 232448, "shared memory budget (227 KB per CTA)");
 };
 
@@ -372,27 +372,35 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
             } else {
                 // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
-                uint32_t vals[CW / 4];   // packed 16-bit pairs: 8 registers per 32 columns
-                uint32_t meta[CW / 32];  // codes of 8 groups, group g in bits 4g..4g+3
+                constexpr int NCH = CW / 32;     // 32-column chunks of this warp
+                constexpr int NPAIR = NCH / 2;   // pairs of chunks (64 columns, one load round trip)
+                uint32_t vals[CW / 4];           // packed 16-bit pairs: 8 registers per chunk
+                uint32_t meta[NCH];              // codes of 8 groups, group g in bits 4g..4g+3
+                auto prune_chunk = [&](const uint32_t* r, int c) {
+                    uint32_t m = 0;
 #pragma unroll
-                for (int c2 = 0; c2 < CW / 64; ++c2) {
-                    uint32_t r[64];   // one load round trip per 64 columns (the metadata unit)
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        float v0, v1;
+                        const uint32_t code = prune_group_f32(__uint_as_float(r[4 * g4]), __uint_as_float(r[4 * g4 + 1]),
+                                                              __uint_as_float(r[4 * g4 + 2]), __uint_as_float(r[4 * g4 + 3]), v0, v1);
+                        vals[c * 8 + g4] = pack2(v0, v1, p.bf16);   // rounded after selection (10.1_prune_acc.py:241)
+                        m |= code << (4 * g4);
+                    }
+                    meta[c] = m;
+                };
+#pragma unroll
+                for (int c2 = 0; c2 < NPAIR; ++c2) {
+                    uint32_t r[64];
                     tc_ld_32x32b_x64(tacc + (uint32_t)(c2 * 64), r);
                     tc_wait_ld();
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int c = 2 * c2 + h;
-                        uint32_t m = 0;
-#pragma unroll
-                        for (int g4 = 0; g4 < 8; ++g4) {
-                            float v0, v1;
-                            const uint32_t code = prune_group_f32(__uint_as_float(r[32 * h + 4 * g4]), __uint_as_float(r[32 * h + 4 * g4 + 1]),
-                                                                  __uint_as_float(r[32 * h + 4 * g4 + 2]), __uint_as_float(r[32 * h + 4 * g4 + 3]), v0, v1);
-                            vals[c * 8 + g4] = pack2(v0, v1, p.bf16);   // rounded after selection (10.1_prune_acc.py:241)
-                            m |= code << (4 * g4);
-                        }
-                        meta[c] = m;
-                    }
+                    prune_chunk(r, 2 * c2);
+                    prune_chunk(r + 32, 2 * c2 + 1);
+                }
+                if constexpr (NCH % 2 == 1) {
+                    uint32_t r[32];
+                    tc_ld_32x32b_x32(tacc + (uint32_t)((NCH - 1) * 32), r);
+                    tc_wait_ld();
+                    prune_chunk(r, NCH - 1);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -402,7 +410,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (row_ok) {
                     uint16_t* vrow = static_cast<uint16_t*>(p.c_vals) + row * (int64_t)(p.N / 2) + col0 / 2;
 #pragma unroll
-                    for (int c = 0; c < CW / 32; ++c) {
+                    for (int c = 0; c < NCH; ++c) {
                         if (col0 + c * 32 < p.N) {
                             *reinterpret_cast<uint4*>(vrow + c * 16) =
                                 make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
@@ -411,40 +419,40 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         }
                     }
                 }
-                // metadata words pair row r (low half) with row r+8 (high half): lanes l and l^8 of this
-                // warp.  Per 64 columns the lane with bit 3 clear assembles the two words of the first 32
-                // columns, its partner those of the second 32, so each writes 8 adjacent bytes.
+                // Metadata words pair row r (low half) with row r+8 (high half): lanes l and l^8 of this
+                // warp.  A 32-column chunk gives two words (16 columns each).  Chunks are handled in
+                // pairs: the lane with bit 3 clear assembles the two words of the first chunk, its
+                // partner those of the second, so each writes 8 adjacent bytes; an odd last chunk is
+                // written by the lower lanes alone.
                 const bool upper = (lane & 8) != 0;
                 const int m0 = lane & 7;
                 const int64_t row16 = row >> 4;
+                auto write_words = [&](uint32_t w0, uint32_t w1, int ncol) {   // ncol: first column of w0
+                    if (!row_ok || ncol >= p.N) return;
+                    const int cidx = ncol >> 4;                                  // logical metadata column of w0
+                    if (p.c_meta_ref != nullptr) {
+                        uint32_t* e = p.c_meta_ref + row16 * (int64_t)(p.N / 2) + (cidx >> 2) * 32 + m0 * 4 + (cidx & 3);
+                        *reinterpret_cast<uint2*>(e) = make_uint2(w0, w1);
+                    }
+                    if (p.c_meta_tc != nullptr) {
+                        const int64_t t128 = row >> 7;
+                        const int m2 = (int)((row >> 4) & 7);
+                        const int kb = cidx >> 3, j = (cidx & 7) >> 1;
+                        uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)(p.N >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
+                        rec[0] = w0;
+                        rec[32] = w1;
+                    }
+                };
 #pragma unroll
-                for (int c2 = 0; c2 < CW / 64; ++c2) {
+                for (int c2 = 0; c2 < NPAIR; ++c2) {
                     const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2], 8);
                     const uint32_t xb = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2 + 1], 8);
-                    uint32_t w0, w1;  // logical columns c and c+1 (16 columns each) of rows (r, r+8)
-                    if (!upper) {
-                        w0 = __byte_perm(meta[2 * c2], xa, 0x5410);
-                        w1 = __byte_perm(meta[2 * c2], xa, 0x7632);
-                    } else {
-                        w0 = __byte_perm(xb, meta[2 * c2 + 1], 0x5410);
-                        w1 = __byte_perm(xb, meta[2 * c2 + 1], 0x7632);
-                    }
-                    const int ncol = col0 + c2 * 64 + (upper ? 32 : 0);   // first column these two words describe
-                    if (row_ok && ncol < p.N) {
-                        const int cidx = ncol >> 4;                        // logical metadata column of w0
-                        if (p.c_meta_ref != nullptr) {
-                            uint32_t* e = p.c_meta_ref + row16 * (int64_t)(p.N / 2) + (cidx >> 2) * 32 + m0 * 4 + (cidx & 3);
-                            *reinterpret_cast<uint2*>(e) = make_uint2(w0, w1);
-                        }
-                        if (p.c_meta_tc != nullptr) {
-                            const int64_t t128 = row >> 7;
-                            const int m2 = (int)((row >> 4) & 7);
-                            const int kb = cidx >> 3, j = (cidx & 7) >> 1;
-                            uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)(p.N >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
-                            rec[0] = w0;
-                            rec[32] = w1;
-                        }
-                    }
+                    if (!upper) write_words(__byte_perm(meta[2 * c2], xa, 0x5410), __byte_perm(meta[2 * c2], xa, 0x7632), col0 + c2 * 64);
+                    else write_words(__byte_perm(xb, meta[2 * c2 + 1], 0x5410), __byte_perm(xb, meta[2 * c2 + 1], 0x7632), col0 + c2 * 64 + 32);
+                }
+                if constexpr (NCH % 2 == 1) {
+                    const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[NCH - 1], 8);
+                    if (!upper) write_words(__byte_perm(meta[NCH - 1], xa, 0x5410), __byte_perm(meta[NCH - 1], xa, 0x7632), col0 + (NCH - 1) * 32);
                 }
             }
             if (++a == ACC) { a = 0; acc_phase ^= 1u; }
@@ -621,7 +629,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     // when they fill the last wave better.
     if (bm == 0 && bn == 0) {
         struct Cand { int bm, bn, g; double eff; bool plain_only; };
-        const Cand cands[4] = {{512, 224, 2, 1.00, true}, {256, 256, 2, 0.97, false}, {256, 128, 2, 0.78, false},
+        const Cand cands[4] = {{512, 224, 2, 1.00, false}, {256, 256, 2, 0.97, false}, {256, 128, 2, 0.78, false},
                                {128, 128, 1, 0.55, false}};
         double best = -1.0;
         for (const Cand& c : cands) {
@@ -639,6 +647,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     if (bm == 0) bm = (M % 256 == 0 || M > 1024) ? 256 : 128;
     if (bn == 0) bn = (bm == 512) ? 224 : ((bm == 256 && N >= 256) ? 256 : 128);
     if (prune_out) {
+        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, true, 2>>(g, stream);
         if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, true>>(g, stream);
         if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, true>>(g, stream);
         if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, true>>(g, stream);
@@ -648,7 +657,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
         if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6>>(g, stream);
         if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4>>(g, stream);
     }
-    return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 512x224 [plain GEMM only], 256x256, 256x128, 128x128)", who, bm, bn);
+    return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 512x224, 256x256, 256x128, 128x128)", who, bm, bn);
 }
 
 }  // namespace s24
