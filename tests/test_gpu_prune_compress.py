@@ -188,3 +188,27 @@ def test_full_size_properties(mods, dtype):
         assert np.array_equal(bits(p[r0:r0 + 128]), want_p)
         assert np.array_equal(bits(v[r0:r0 + 128]), want_v)
         assert np.array_equal(e[r0 // 16:r0 // 16 + 8].cpu().numpy(), want_e)
+
+
+def test_index_arithmetic_beyond_2_31_elements(mods):
+    """49152 x 49152 has 2.4e9 elements: element offsets no longer fit 32 bits.  Check the last
+    row panels (whose offsets are the largest) against the CPU oracle, bit for bit."""
+    s24 = mods["s24"]
+    M = K = 49152
+    A = torch.empty(M, K, dtype=torch.float16, device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(49152)
+    for r0 in range(0, M, 8192):          # generate in slabs to bound the fp32 temporary
+        A[r0:r0 + 8192] = torch.randn(8192, K, generator=g, device=DEV, dtype=torch.float32).to(torch.float16)
+    v, e, tc = s24.prune_compress(A, want_ref=True, want_tc=True)
+    for r0 in (0, 43776, M - 128):        # 43776 * 49152 > 2^31
+        ab = bits(A[r0:r0 + 128])
+        want_p = oracle.prune(ab, oracle.FP16)
+        want_v, want_ml, want_e = oracle.compress(want_p, oracle.FP16)
+        assert np.array_equal(bits(v[r0:r0 + 128]), want_v)
+        assert np.array_equal(e[r0 // 16:r0 // 16 + 8].cpu().numpy(), want_e)
+        rec = (K // 128) * 512
+        got_tc = tc[(r0 // 128) * rec:(r0 // 128 + 1) * rec].cpu().numpy().view(np.uint32)
+        assert np.array_equal(got_tc, oracle.meta_tc(want_ml, K))
+    del v, e, tc
+    p = s24.prune(A[M - 4096:])
+    assert np.array_equal(bits(p[-128:]), oracle.prune(bits(A[M - 128:]), oracle.FP16))

@@ -59,7 +59,7 @@ def test_identity_b_reveals_decompressed_a(mods, cfg):
     assert torch.equal(C.float().cpu(), from_bits(ap, torch.float16).float())   # -0.0 == +0.0
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 8, 128), (256, 24, 256), (256, 256, 512), (384, 200, 384), (512, 1032, 1280), (1024, 768, 2048)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 8, 128), (256, 24, 256), (256, 256, 512), (384, 200, 384), (512, 1032, 1280), (1024, 768, 2048), (256, 256, 16384), (4096, 128, 256)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
 def test_spmm_vs_fp32_reference(mods, M, N, K, dtype, cfg):
