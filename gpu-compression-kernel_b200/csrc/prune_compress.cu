@@ -39,6 +39,12 @@ __device__ __forceinline__ void ld128x2(const void* p, uint32_t (&r)[8])
                  : "l"(static_cast<const char*>(p) + 16));
 }
 
+__device__ __forceinline__ void st128x2(void* p, const uint32_t (&r)[8])
+{
+    *reinterpret_cast<uint4*>(p) = make_uint4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<uint4*>(static_cast<char*>(p) + 16) = make_uint4(r[4], r[5], r[6], r[7]);
+}
+
 __device__ __forceinline__ void st256(void* p, const uint32_t (&r)[8])
 {
     asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r[0]), "r"(r[1]),
@@ -102,8 +108,13 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
     const uint32_t mb = row_span<DT, MODE>(b_lo, b_hi, p.tie, vb);
 
     const int64_t half_k = p.K >> 1;
-    st256(p.vals + rA * half_k + (col0 >> 1), va);
-    st256(p.vals + rB * half_k + (col0 >> 1), vb);
+    if (LD256) {   // 256-bit accesses need 32-byte alignment of A, its row stride and vals
+        st256(p.vals + rA * half_k + (col0 >> 1), va);
+        st256(p.vals + rB * half_k + (col0 >> 1), vb);
+    } else {
+        st128x2(p.vals + rA * half_k + (col0 >> 1), va);
+        st128x2(p.vals + rB * half_k + (col0 >> 1), vb);
+    }
 
     // metadata words: row r in the low half, row r+8 in the high half; k1 = which 16-column half
     const uint32_t w0 = __byte_perm(ma, mb, 0x5410);
@@ -206,8 +217,8 @@ static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld
     if (ld < K || ld % 8 != 0) return fail(S24_ERR_SHAPE, "prune_compress: row stride %lld must be >= K and a multiple of 8", (long long)ld);
     if (meta_tc != nullptr && (M % 128 != 0 || K % 128 != 0))
         return fail(S24_ERR_SHAPE, "prune_compress: tensor-core metadata needs M %% 128 == 0 and K %% 128 == 0 (got %lld x %lld)", (long long)M, (long long)K);
-    if (!aligned(A, 16) || !aligned(vals, 32) || !aligned(meta_ref, 16) || !aligned(meta_tc, 16))
-        return fail(S24_ERR_INVALID_ARG, "prune_compress: pointers must be 16-byte aligned (vals 32)");
+    if (!aligned(A, 16) || !aligned(vals, 16) || !aligned(meta_ref, 16) || !aligned(meta_tc, 16))
+        return fail(S24_ERR_INVALID_ARG, "prune_compress: pointers must be 16-byte aligned");
     if (M == 0 || K == 0) return S24_OK;
 
     PcParams p;
@@ -223,7 +234,7 @@ static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld
     p.warp_tiles = (M / 16) * p.col_blocks;
     const int64_t blocks = (p.warp_tiles + 7) / 8;
     if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "prune_compress: matrix too large for one launch");
-    const bool ld256ok = aligned(A, 32) && (ld % 16 == 0);
+    const bool ld256ok = aligned(A, 32) && aligned(vals, 32) && (ld % 16 == 0);
     dim3 grid((unsigned)blocks), block(256);
 #define S24_LAUNCH_PC(DT, MODE)                                                              \
     do {                                                                                     \

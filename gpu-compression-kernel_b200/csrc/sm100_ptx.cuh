@@ -273,13 +273,14 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
     return d;
 }
 
-// Instruction descriptor for tcgen05.mma(.sp).kind::f16: fp32 accumulate, A K-major,
-// B MN-major (row-major (K, N) in memory), 2:4 sparse A.
+// Instruction descriptor for tcgen05.mma(.sp).kind::f16: fp32 accumulate, A K-major, 2:4 sparse A;
+// B either MN-major (row-major (K, N) in memory, b_mn_major = 1) or K-major (row-major (N, K),
+// i.e. B given transposed, b_mn_major = 0).
 //   bits 0-1 sparsity selector, 2 sparse, 4-5 D format (1 = f32), 7-9 A format, 10-12 B format
 //   (0 = f16, 1 = bf16), 15 A major (0 = K), 16 B major (1 = MN), 17-22 N >> 3, 24-28 M >> 4
-__host__ __device__ constexpr uint32_t make_idesc_sp_f16(int bf16, int m, int n)
+__host__ __device__ constexpr uint32_t make_idesc_sp_f16(int bf16, int m, int n, int b_mn_major = 1)
 {
-    return (1u << 2) | (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | (0u << 15) | (1u << 16) |
+    return (1u << 2) | (1u << 4) | ((uint32_t)bf16 << 7) | ((uint32_t)bf16 << 10) | (0u << 15) | ((uint32_t)b_mn_major << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 

@@ -50,9 +50,12 @@ constexpr uint32_t kTmemCols = 512;
 // G = CTAs per tile engine (1 or a pair), BN = tile columns, MT = 128-row sub-tiles per CTA:
 // with MT = 2 a CTA pair owns 512 rows as two 256-row MMAs that share every B stage, which cuts
 // the bytes brought into each SM per flop by a quarter and deepens the ring in MMA time.
-template <int G, int BN, int STAGES, bool PRUNE_OUT = false, int MT = 1>
+// BT: B is given transposed, (N, K) row-major (activations stored (tokens, hidden)); its tiles are
+// then K-major in shared memory like A's, loaded as two 64-wide K atoms per stage.
+template <int G, int BN, int STAGES, bool PRUNE_OUT = false, int MT = 1, bool BT = false>
 struct GemmCfg {
     static constexpr bool kPruneOut = PRUNE_OUT;
+    static constexpr bool kBT = BT;
     static constexpr int kG = G;
     static constexpr int kBN = BN;
     static constexpr int kMT = MT;
@@ -63,10 +66,13 @@ struct GemmCfg {
     static constexpr int kABytes = MT * kASubBytes;
     static constexpr int kBAtomBytes = kBlockK * 128;           // 128 k-rows x 64 columns x 2 B
     static constexpr int kBAtoms = (kBNCta + 63) / 64;          // loaded as whole 64-column atoms
-    static constexpr int kBBytes = kBAtoms * kBAtomBytes;
+    static constexpr int kBBytes = kBAtoms * kBAtomBytes;      // shared-memory footprint of a B stage
+    static constexpr int kBtAtomBytes = kBNCta * 128;           // transposed B: N rows x 64 k-values x 2 B
+    static constexpr int kBLoadBytes = BT ? 2 * kBtAtomBytes : kBBytes;   // bytes the copies deliver
     static constexpr int kESubBytes = 2048;
     static constexpr int kEBytes = MT * kESubBytes;
     static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;
+    static constexpr int kStageTxBytes = kABytes + kBLoadBytes + kEBytes;
     static constexpr int kAccCols = BN * MT;                    // one accumulator set
     static constexpr int kAccStages = (kAccCols >= 256) ? 1 : 2;
     static constexpr int kECol0 = kAccStages * kAccCols;        // metadata columns follow the accumulators
@@ -214,7 +220,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     // leader's barrier too (its byte count may run ahead of the announcement, which
                     // the transaction count tolerates)
                     if (leader)
-                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * Cfg::kStageBytes));
+                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * Cfg::kStageTxBytes));
                     const uint32_t a_dst = smem_a + s * Cfg::kABytes;
                     const uint32_t b_dst = smem_b + s * Cfg::kBBytes;
                     const uint32_t e_dst = smem_e + s * Cfg::kEBytes;
@@ -230,10 +236,19 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             tma_load_2d(e_dst + m * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
                         }
                     }
+                    if constexpr (Cfg::kBT) {
+                        // transposed B: two boxes of (64 k-values x kBNCta rows of N)
 #pragma unroll
-                    for (int i = 0; i < Cfg::kBAtoms; ++i) {
-                        if (G == 2) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                        else tma_load_2d(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        for (int h = 0; h < 2; ++h) {
+                            if (G == 2) tma_load_2d_pair(b_dst + h * Cfg::kBtAtomBytes, &tm_b, kb * kBlockK + 64 * h, col0, full);
+                            else tma_load_2d(b_dst + h * Cfg::kBtAtomBytes, &tm_b, kb * kBlockK + 64 * h, col0, full);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < Cfg::kBAtoms; ++i) {
+                            if (G == 2) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                            else tma_load_2d(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                        }
                     }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
@@ -242,7 +257,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (leader && elect_one()) {
-            const uint32_t idesc = make_idesc_sp_f16(p.bf16, kRowsPerCta * G, BN);
+            const uint32_t idesc = make_idesc_sp_f16(p.bf16, kRowsPerCta * G, BN, Cfg::kBT ? 0 : 1);
             int s = 0, a = 0;
             uint32_t phase = 0, acc_phase = 0;
             for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
@@ -277,9 +292,15 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         // metadata column j (even column address + selector bit); the sub-tiles reuse
                         // the same B slice back to back
 #pragma unroll
+                        // transposed B is K-major like A: 64 bytes per K = 32 step inside a 128-byte row,
+                        // the second pair of steps in the second 64-wide K atom
+                        const uint64_t bstep = Cfg::kBT
+                            ? make_smem_desc(smem_b + s * Cfg::kBBytes + (j >> 1) * Cfg::kBtAtomBytes + (j & 1) * 64, 16, 1024, kSwizzle128B)
+                            : bdesc + (uint64_t)(j * 256);
+#pragma unroll
                         for (int m = 0; m < MT; ++m)
                             tc_mma_sp_f16<G>(tmem_d + (uint32_t)(m * BN), adesc + (uint64_t)(m * (Cfg::kASubBytes >> 4) + j * 2),
-                                             bdesc + (uint64_t)(j * 256), idesc | (uint32_t)(j & 1),
+                                             bstep, idesc | (uint32_t)(j & 1),
                                              e_cols + (uint32_t)(4 * m + (j & 2)), (kb | j) != 0 ? 1u : 0u);
                     }
                     if (G == 2) tc_commit_pair(bar_empty + 8 * s, 3);
@@ -506,6 +527,7 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_byte
 }
 
 struct GemmArgs {
+    bool bt;   // B given transposed: (N, K) row-major, ldb = its row stride
     const void* vals;
     const void* meta_tc;
     const void* B;
@@ -522,8 +544,12 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
     int rc = make_map_2d(&tm_a, dt, 2, g.vals, (uint64_t)(g.K / 2), (uint64_t)g.M, (uint64_t)g.K, 64, kRowsPerCta,
                          CU_TENSOR_MAP_SWIZZLE_128B, "A values");
     if (rc) return rc;
-    rc = make_map_2d(&tm_b, dt, 2, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, kBlockK,
-                     CU_TENSOR_MAP_SWIZZLE_128B, "B");
+    if (Cfg::kBT)
+        rc = make_map_2d(&tm_b, dt, 2, g.B, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb * 2, 64, Cfg::kBNCta,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "B (transposed)");
+    else
+        rc = make_map_2d(&tm_b, dt, 2, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, kBlockK,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "B");
     if (rc) return rc;
     const uint64_t records = (uint64_t)(g.M / 128) * (uint64_t)(g.K / 128);
     rc = make_map_2d(&tm_e, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, g.meta_tc, 128, records * 4, 512, 128, 4,
@@ -581,9 +607,11 @@ static int* status_word_address()
 
 static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                     int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, cudaStream_t stream,
-                    bool prune_out = false, void* c_vals = nullptr, void* c_meta_ref = nullptr, void* c_meta_tc = nullptr)
+                    bool prune_out = false, void* c_vals = nullptr, void* c_meta_ref = nullptr, void* c_meta_tc = nullptr,
+                    bool bt = false)
 {
-    const char* who = prune_out ? "spmm_prune_out" : "spmm";
+    const char* who = prune_out ? "spmm_prune_out" : (bt ? "spmm_bt" : "spmm");
+    if (bt && prune_out) return fail(S24_ERR_UNSUPPORTED, "spmm_prune_out: transposed B is not supported");
     if (vals == nullptr || meta_tc == nullptr || B == nullptr || (!prune_out && C == nullptr) || (prune_out && c_vals == nullptr))
         return fail(S24_ERR_INVALID_ARG, "%s: null pointer", who);
     if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "%s: bad dtype %d", who, dtype);
@@ -593,7 +621,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     if (prune_out && N % 128 != 0)
         return fail(S24_ERR_SHAPE, "%s: needs N %% 128 == 0 (got N=%lld)", who, (long long)N);
     if (M > 0x7FFFFF00ll || N > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return fail(S24_ERR_SHAPE, "%s: dimension too large", who);
-    if (ldb < N || ldb % 8 != 0 || (!prune_out && (ldc < N || ldc % 8 != 0)))
+    if (ldb < (bt ? K : N) || ldb % 8 != 0 || (!prune_out && (ldc < N || ldc % 8 != 0)))
         return fail(S24_ERR_SHAPE, "%s: ldb/ldc must be >= N and multiples of 8 (got %lld, %lld)", who, (long long)ldb, (long long)ldc);
     if (!aligned(vals, 16) || !aligned(meta_tc, 16) || !aligned(B, 16) || !aligned(C, 16) || !aligned(c_vals, 16) ||
         !aligned(c_meta_ref, 16) || !aligned(c_meta_tc, 16))
@@ -609,6 +637,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.N = N;
     g.K = K;
     g.ldb = ldb;
+    g.bt = bt;
     g.dtype = dtype;
     g.p.C = C;
     g.p.ldc = ldc;
@@ -651,6 +680,11 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
         if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, true>>(g, stream);
         if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, true>>(g, stream);
         if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, true>>(g, stream);
+    } else if (bt) {
+        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, false, 2, true>>(g, stream);
+        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, false, 1, true>>(g, stream);
+        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, false, 1, true>>(g, stream);
+        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, false, 1, true>>(g, stream);
     } else {
         if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, false, 2>>(g, stream);
         if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4>>(g, stream);
@@ -668,6 +702,13 @@ extern "C" int s24_spmm(const void* vals, const void* meta_tc, const void* B, vo
                         int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, void* stream)
 {
     return run_spmm(vals, meta_tc, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s24_spmm_bt(const void* vals, const void* meta_tc, const void* Bt, void* C, int64_t M, int64_t N, int64_t K,
+                           int64_t ldbt, int64_t ldc, int dtype, const s24_tile_cfg* cfg, void* stream)
+{
+    return run_spmm(vals, meta_tc, Bt, C, M, N, K, ldbt, ldc, dtype, cfg, static_cast<cudaStream_t>(stream), false, nullptr,
+                    nullptr, nullptr, true);
 }
 
 extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const void* B, void* C, int64_t M, int64_t N,

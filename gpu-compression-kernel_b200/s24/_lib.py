@@ -32,6 +32,7 @@ SIGNATURES = {
     "s24_meta_tc_bytes": (_sz, [_i64, _i64]),
     "s24_meta_convert": (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),
     "s24_spmm": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, ctypes.POINTER(TileCfg), _vp]),
+    "s24_spmm_bt": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, ctypes.POINTER(TileCfg), _vp]),
     "s24_spmm_ref_meta": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
                                  ctypes.POINTER(TileCfg), _vp, _sz, _vp]),
     "s24_spmm_ref_meta_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,

@@ -229,11 +229,34 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
 
     meta_layout "tc": `meta` is the tensor-core layout.  "ref": `meta` is the reference's
     E (M/16, K) int16; it is re-laid into `workspace` (allocated here if not given) first.
+
+    B is (K, N).  If it is the transposed view of a row-major (N, K) tensor (`X.t()` of
+    activations stored (tokens, hidden)) it is used in place through `s24_spmm_bt`; any other
+    non-row-major B is copied to row-major first.
     """
     _require_cuda(vals, meta, B)
     M, N, K = _check_gemm(vals, B)
     v = vals.contiguous()
+    bt = (B.stride(0) == 1 and B.stride(1) >= K and B.stride(1) % 8 == 0 and B.data_ptr() % 16 == 0
+          and not (B.stride(1) == 1 and B.stride(0) >= N))
+    if bt:
+        if meta_layout == "ref":
+            if meta.numel() != M * K // 16:
+                raise RuntimeError(f"E has {meta.numel()} elements, expected {M * K // 16} for ({M}, {K})")
+            meta = meta_convert(meta, "ref", "tc", M, K)
+        c = out if out is not None else torch.empty((M, N), dtype=vals.dtype, device=vals.device)
+        if c.stride(1) != 1 or c.stride(0) % 8 != 0 or tuple(c.shape) != (M, N) or c.dtype != vals.dtype:
+            raise RuntimeError(f"`out` must be a row-major ({M}, {N}) {vals.dtype} tensor")
+        with _on_device(vals):
+            L.check(L.lib().s24_spmm_bt(_p(v), _p(meta), _p(B), _p(c), M, N, K, B.stride(1), c.stride(0),
+                                        _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
+        return c
     b = _row_major(B)
+    if out is not None:
+        if (tuple(out.shape) != (M, N) or out.dtype != vals.dtype or out.device != vals.device or out.stride(1) != 1
+                or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0):
+            raise RuntimeError(f"`out` must be a ({M}, {N}) {vals.dtype} tensor on {vals.device} with unit column "
+                               "stride, a row stride that is a multiple of 8 and 16-byte alignment")
     c = out if out is not None else torch.empty((M, N), dtype=vals.dtype, device=vals.device)
     with _on_device(vals):
         if meta_layout == "ref" and autotune and manual_config is None:

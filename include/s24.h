@@ -17,6 +17,7 @@
  *   s24_meta_convert     compression/compress_2_4.py:6-30     _calculate_meta_reordering_offsets
  *   s24_spmm             compression/gluon_ws_sparse.py:244-278,560-613  run_sparse_ws_matmul
  *   s24_spmm_ref_meta    same launcher, fed the reference's metadata layout directly
+ *   s24_spmm_bt          same launcher, B given transposed ((N, K) row-major)
  *   s24_spmm_prune_out   compression/kernels/10.1_prune_acc.py:88-154,359-398,624-678
  *
  * Element types: S24_FP16 / S24_BF16, 16-bit storage, row-major matrices.
@@ -142,6 +143,17 @@ S24_API int s24_meta_convert(const void* src, int from_layout, void* dst, int to
 S24_API int s24_spmm(const void* vals, const void* meta_tc, const void* B, void* C,
              int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,
              const s24_tile_cfg* cfg, void* stream);
+
+/*
+ * The same product with B given transposed: Bt is (N, K) row-major with row stride ldbt, i.e.
+ * C = A24 . Bt^T.  This is the layout of activations stored (tokens, hidden) when the sparse
+ * operand is a weight; the reference's launcher takes (K, N) row-major only
+ * (compression/gluon_ws_sparse.py:522-525,563) and a caller would have to transpose first.
+ * Same rules as s24_spmm with ldbt >= K, ldbt % 8 == 0.
+ */
+S24_API int s24_spmm_bt(const void* vals, const void* meta_tc, const void* Bt, void* C,
+                int64_t M, int64_t N, int64_t K, int64_t ldbt, int64_t ldc, int dtype,
+                const s24_tile_cfg* cfg, void* stream);
 
 /*
  * Same product with the metadata in the reference's layout (the E a caller of

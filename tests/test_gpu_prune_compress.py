@@ -212,3 +212,24 @@ def test_index_arithmetic_beyond_2_31_elements(mods):
     del v, e, tc
     p = s24.prune(A[M - 4096:])
     assert np.array_equal(bits(p[-128:]), oracle.prune(bits(A[M - 128:]), oracle.FP16))
+
+
+def test_sixteen_byte_aligned_views_take_the_narrow_access_path(mods):
+    """A and the values buffer only 16-byte aligned (a view 8 elements into a row): the kernel must
+    fall back from 256-bit to 128-bit accesses and still be bit-exact"""
+    import ctypes
+    from s24 import _lib
+    M, K = 64, 256
+    big = randn((M, K + 16), torch.float16, 17).to(DEV)
+    A = big[:, 8:8 + K]                                   # 16-byte aligned start, row stride K + 16
+    vals_store = torch.empty(M * (K // 2) + 8, dtype=torch.float16, device=DEV)
+    vals = vals_store[8:]                                 # 16-byte aligned, not 32
+    assert A.data_ptr() % 32 == 16 and vals.data_ptr() % 32 == 16
+    e = torch.empty(M // 16, K, dtype=torch.int16, device=DEV)
+    rc = _lib.lib().s24_prune_compress(ctypes.c_void_p(A.data_ptr()), M, K, K + 16, _lib.FP16, _lib.MODE_SIGNED,
+                                       _lib.TIE_REFERENCE, ctypes.c_void_p(vals.data_ptr()), ctypes.c_void_p(e.data_ptr()),
+                                       None, None)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    want_v, _, want_e = oracle.compress(oracle.prune(bits(A), oracle.FP16), oracle.FP16)
+    assert np.array_equal(bits(vals.view(M, K // 2)), want_v) and np.array_equal(e.cpu().numpy(), want_e)

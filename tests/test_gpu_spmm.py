@@ -205,3 +205,29 @@ def test_launchers_can_be_captured_in_a_cuda_graph(mods):
     torch.cuda.synchronize()
     _status_ok(s24)
     assert torch.equal(c1, eager) and torch.equal(c2, eager)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 200, 384), (512, 1032, 1280), (1024, 2048, 4096)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
+def test_transposed_b_is_used_in_place(mods, M, N, K, dtype, cfg):
+    """B passed as X.t() with X (N, K) row-major (activations stored (tokens, hidden)): the kernel
+    reads X directly as a K-major operand; the result must equal the row-major-B product bit for bit"""
+    s24 = mods["s24"]
+    A, B, ap, vals, ml, e = _prepare(M, K, N, dtype, 300 + M + N + K)
+    tc = torch.from_numpy(oracle.meta_tc(ml, K).view(np.int32)).to(DEV)
+    v = from_bits(vals, dtype, DEV)
+    Bd = B.to(DEV)
+    X = Bd.t().contiguous()                      # (N, K) row-major
+    assert X.t().stride(0) == 1
+    C_t = s24.spmm(v, tc, X.t(), manual_config=cfg)
+    _status_ok(s24)
+    _check(C_t, _reference(ap, B, dtype))
+    C_n = s24.spmm(v, tc, Bd, manual_config=cfg)
+    assert torch.equal(C_t, C_n)
+    # padded rows (row stride > K) and the reference-layout metadata entry
+    Xp = torch.zeros(N, K + 64, dtype=dtype, device=DEV)
+    Xp[:, :K] = X
+    E = torch.from_numpy(e).to(DEV)
+    C_p = s24.spmm(v, E, Xp[:, :K].t(), meta_layout="ref", manual_config=cfg)
+    assert torch.equal(C_p, C_n)
