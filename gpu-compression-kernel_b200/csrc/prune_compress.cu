@@ -202,6 +202,25 @@ __global__ void __launch_bounds__(256) meta_convert_kernel(const uint16_t* __res
     }
 }
 
+// ---------------------------------------------------------------- gathered shards -> row-major
+
+// An all-gather of column shards arrives shard-major, (G, rows, nl); the caller wants (rows, G*nl).
+// One 16-byte vector per thread, consecutive threads write consecutive output addresses and read
+// whole 16-byte pieces of one shard row.
+__global__ void __launch_bounds__(256) relayout_shards_kernel(const uint4* __restrict__ stage, uint4* __restrict__ out,
+                                                              int64_t rows, int64_t shards, int64_t vec_per_shard_row,
+                                                              int64_t out_row_vecs)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t per_row = shards * vec_per_shard_row;
+    if (idx >= rows * per_row) return;
+    const int64_t r = idx / per_row;
+    const int64_t c = idx - r * per_row;
+    const int64_t g = c / vec_per_shard_row;
+    const int64_t j = c - g * vec_per_shard_row;
+    out[r * out_row_vecs + c] = stage[(g * rows + r) * vec_per_shard_row + j];
+}
+
 // ---------------------------------------------------------------- host launchers
 
 static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld, int dtype, int mode, int tie,
@@ -332,4 +351,20 @@ extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int
     meta_convert_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(src), from_layout, static_cast<uint16_t*>(dst), to_layout, M, ncols);
     return check_cuda(cudaGetLastError(), "meta_convert launch");
+}
+
+extern "C" int s24_relayout_shards(const void* stage, void* out, int64_t rows, int64_t shards, int64_t shard_cols,
+                                   int64_t ldo, void* stream)
+{
+    if (stage == nullptr || out == nullptr) return fail(S24_ERR_INVALID_ARG, "relayout_shards: null pointer");
+    if (rows < 0 || shards <= 0 || shard_cols <= 0 || shard_cols % 8 != 0 || ldo % 8 != 0 || ldo < shards * shard_cols)
+        return fail(S24_ERR_SHAPE, "relayout_shards: needs shard_cols %% 8 == 0, ldo %% 8 == 0 and ldo >= shards * shard_cols");
+    if (!aligned(stage, 16) || !aligned(out, 16)) return fail(S24_ERR_INVALID_ARG, "relayout_shards: pointers must be 16-byte aligned");
+    const int64_t vecs = rows * shards * (shard_cols / 8);
+    if (vecs == 0) return S24_OK;
+    const int64_t blocks = (vecs + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "relayout_shards: too large for one launch");
+    relayout_shards_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(stage), static_cast<uint4*>(out), rows, shards, shard_cols / 8, ldo / 8);
+    return check_cuda(cudaGetLastError(), "relayout_shards launch");
 }

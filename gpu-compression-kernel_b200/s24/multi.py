@@ -112,7 +112,7 @@ class NShardedSpmm:
                 with torch.cuda.stream(self._comm_stream):
                     self._comm_stream.wait_event(ev)
                     dist.all_gather_into_tensor(stage, c_local.contiguous(), group=self.group)
-                    out_v[r0:r1].copy_(stage.view(G, rows, nl).permute(1, 0, 2))   # shard-major -> row-major
+                    self._relayout(stage.view(G, rows, nl), out[r0:r1])             # shard-major -> row-major
                     done = torch.cuda.Event()
                     done.record(self._comm_stream)
                 pending.append((done, stage, c_local))
@@ -123,6 +123,15 @@ class NShardedSpmm:
             for done, _, _ in pending:
                 compute.wait_event(done)
         return out
+
+    @staticmethod
+    def _relayout(stage3: torch.Tensor, out_rows: torch.Tensor) -> None:
+        if stage3.is_cuda and stage3.element_size() == 2 and stage3.shape[2] % 8 == 0:
+            from . import ops
+            ops.relayout_shards(stage3, out_rows)          # the library's copy kernel
+        else:                                              # CPU ranks in tests
+            G, rows, nl = stage3.shape
+            out_rows.view(rows, G, nl).copy_(stage3.permute(1, 0, 2))
 
     def _meta_rows(self, r0: int, r1: int) -> torch.Tensor:
         """tensor-core metadata of rows [r0, r1): records are ordered [row tile of 128][k block],

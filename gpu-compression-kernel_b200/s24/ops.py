@@ -310,3 +310,16 @@ def spmm_prune_out(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta
         L.check(L.lib().s24_spmm_prune_out(_p(v), _p(meta_tc), _p(b), _p(cv), _p(ce), _p(ct), M, N, K,
                                            b.stride(0), _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
     return cv, ce, ct
+
+
+def relayout_shards(stage: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """stage (G, rows, nl) shard-major -> out (rows, G * nl) row-major (see s24_relayout_shards)."""
+    _require_cuda(stage, out)
+    G, rows, nl = stage.shape
+    if not stage.is_contiguous() or stage.element_size() != 2 or out.element_size() != 2:
+        raise RuntimeError("relayout_shards needs a contiguous 16-bit (G, rows, nl) stage")
+    if tuple(out.shape) != (rows, G * nl) or out.stride(1) != 1:
+        raise RuntimeError(f"`out` must be ({rows}, {G * nl}) with unit column stride")
+    with _on_device(stage):
+        L.check(L.lib().s24_relayout_shards(_p(stage), _p(out), rows, G, nl, out.stride(0), _stream(stage)))
+    return out

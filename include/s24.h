@@ -209,6 +209,16 @@ S24_API int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void
                        const s24_tile_cfg* cfg, void* stream);
 
 /*
+ * Multi-GPU helper (the reference is single-GPU; no counterpart there).  When C is computed in
+ * column shards, one per rank, an all-gather delivers them shard-major: stage is
+ * (shards, rows, shard_cols) contiguous, 16-bit elements.  This writes the row-major matrix
+ * out[r][g * shard_cols + c] = stage[g][r][c] with row stride ldo (elements).
+ * shard_cols % 8 == 0, ldo % 8 == 0, ldo >= shards * shard_cols, 16-byte aligned pointers.
+ */
+S24_API int s24_relayout_shards(const void* stage, void* out, int64_t rows, int64_t shards, int64_t shard_cols,
+                        int64_t ldo, void* stream);
+
+/*
  * Debug / test aid (no counterpart in the reference): every device-side wait in the GEMM
  * kernels is bounded; if one gives up the kernel records a code and returns.  This call
  * synchronises `stream`, returns S24_OK if no kernel on the current device has reported a

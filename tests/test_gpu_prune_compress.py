@@ -233,3 +233,14 @@ def test_sixteen_byte_aligned_views_take_the_narrow_access_path(mods):
     torch.cuda.synchronize()
     want_v, _, want_e = oracle.compress(oracle.prune(bits(A), oracle.FP16), oracle.FP16)
     assert np.array_equal(bits(vals.view(M, K // 2)), want_v) and np.array_equal(e.cpu().numpy(), want_e)
+
+
+def test_relayout_of_gathered_column_shards(mods):
+    s24 = mods["s24"]
+    G, rows, nl = 4, 96, 72
+    stage = torch.randn(G, rows, nl, device=DEV).to(torch.bfloat16)
+    wide = torch.zeros(rows, G * nl + 8, dtype=torch.bfloat16, device=DEV)
+    out = wide[:, :G * nl]                                   # row stride larger than the logical width
+    s24.relayout_shards(stage, out)
+    assert torch.equal(out, stage.permute(1, 0, 2).reshape(rows, G * nl))
+    assert float(wide[:, G * nl:].abs().max()) == 0
