@@ -291,7 +291,6 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         // K = 32 per instruction: 32 bytes further along A's rows, 32 k-rows (4096 B) into B,
                         // metadata column j (even column address + selector bit); the sub-tiles reuse
                         // the same B slice back to back
-#pragma unroll
                         // transposed B is K-major like A: 64 bytes per K = 32 step inside a 128-byte row,
                         // the second pair of steps in the second 64-wide K atom
                         const uint64_t bstep = Cfg::kBT
