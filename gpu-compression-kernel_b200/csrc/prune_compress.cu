@@ -22,23 +22,6 @@
 
 namespace s24 {
 
-__device__ __forceinline__ void ld256(const void* p, uint32_t (&r)[8])
-{
-    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "l"(p));
-}
-
-__device__ __forceinline__ void ld128x2(const void* p, uint32_t (&r)[8])
-{
-    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "l"(p));
-    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "l"(static_cast<const char*>(p) + 16));
-}
-
 __device__ __forceinline__ void st128x2(void* p, const uint32_t (&r)[8])
 {
     *reinterpret_cast<uint4*>(p) = make_uint4(r[0], r[1], r[2], r[3]);
@@ -63,17 +46,6 @@ struct PcParams {
     int64_t col_blocks;  // ceil(K / 128)
     int64_t warp_tiles;  // (M/16) * col_blocks
 };
-
-// 32 elements of one row -> 16 stored values + 32 metadata bits
-template <int DT, int MODE>
-__device__ __forceinline__ uint32_t row_span(const uint32_t (&lo)[8], const uint32_t (&hi)[8], int tie, uint32_t (&out)[8])
-{
-    const uint32_t c0 = prune_compress_8<DT, MODE>(lo[0], lo[1], lo[2], lo[3], tie, out[0], out[1]);
-    const uint32_t c1 = prune_compress_8<DT, MODE>(lo[4], lo[5], lo[6], lo[7], tie, out[2], out[3]);
-    const uint32_t c2 = prune_compress_8<DT, MODE>(hi[0], hi[1], hi[2], hi[3], tie, out[4], out[5]);
-    const uint32_t c3 = prune_compress_8<DT, MODE>(hi[4], hi[5], hi[6], hi[7], tie, out[6], out[7]);
-    return gather_code_bytes(c0, c1, c2, c3);
-}
 
 template <int DT, int MODE, bool LD256>
 __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)

@@ -340,4 +340,35 @@ S24_HD void prune_8(uint32_t in0, uint32_t in1, uint32_t in2, uint32_t in3, int 
     o3 = byte_perm(p2, p3, 0x7632);
 }
 
+// 32 elements of one row -> 16 stored values + 32 metadata bits
+template <int DT, int MODE>
+S24_HD uint32_t row_span(const uint32_t (&lo)[8], const uint32_t (&hi)[8], int tie, uint32_t (&out)[8])
+{
+    const uint32_t c0 = prune_compress_8<DT, MODE>(lo[0], lo[1], lo[2], lo[3], tie, out[0], out[1]);
+    const uint32_t c1 = prune_compress_8<DT, MODE>(lo[4], lo[5], lo[6], lo[7], tie, out[2], out[3]);
+    const uint32_t c2 = prune_compress_8<DT, MODE>(hi[0], hi[1], hi[2], hi[3], tie, out[4], out[5]);
+    const uint32_t c3 = prune_compress_8<DT, MODE>(hi[4], hi[5], hi[6], hi[7], tie, out[6], out[7]);
+    return gather_code_bytes(c0, c1, c2, c3);
+}
+
+#if defined(__CUDACC__)
+// 32-byte (or 2 x 16-byte) streaming loads of dense input, bypassing L1
+__device__ __forceinline__ void ld256(const void* p, uint32_t (&r)[8])
+{
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+
+__device__ __forceinline__ void ld128x2(const void* p, uint32_t (&r)[8])
+{
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(static_cast<const char*>(p) + 16));
+}
+#endif
+
 }  // namespace s24

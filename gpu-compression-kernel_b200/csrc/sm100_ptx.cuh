@@ -79,6 +79,15 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+// arrive on a barrier of any CTA of the cluster with CTA-scope release only.  For a thread that
+// publishes its own shared-memory stores (already fenced towards the asynchronous proxy) to the
+// MMA issuer of the pair: a cluster-scope release would also wait for every global load this
+// thread still has in flight, once per pipeline stage.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
 // CTA-local arrive + expected byte count (no cluster-scope release: the bytes are delivered by
 // the async proxy, whose completion the barrier itself orders)
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
@@ -111,6 +120,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
         if (globaltimer() - t0 > kWaitTimeoutNs) return false;
     }
 }
+
+// ---------------------------------------------------------------- shared-memory stores by ordinary threads
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// orders this thread's earlier shared-memory stores before later reads by the asynchronous
+// proxy (tcgen05.mma / tcgen05.cp operands, TMA stores)
+__device__ __forceinline__ void fence_proxy_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMA (tensor) loads, no multicast
 

@@ -31,6 +31,7 @@
 // (see s24_device_status), frees its tensor memory and returns.
 #include "s24_common.cuh"
 #include "sm100_ptx.cuh"
+#include "spmm_shared.cuh"
 
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -41,11 +42,7 @@ using namespace ptx;
 
 __device__ int g_status_word = 0;  // first device-side failure since the last s24_device_status()
 
-constexpr int kBlockK = 128;        // logical K per pipeline stage
-constexpr int kRowsPerCta = 128;
-constexpr int kGroupM = 8;          // M-tiles per raster group (compression/common.py:155)
 constexpr int kThreads = 320;       // producer warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
-constexpr uint32_t kTmemCols = 512;
 
 // G = CTAs per tile engine (1 or a pair), BN = tile columns, MT = 128-row sub-tiles per CTA:
 // with MT = 2 a CTA pair owns 512 rows as two 256-row MMAs that share every B stage, which cuts
@@ -82,45 +79,6 @@ struct GemmCfg {
     static_assert(BN % 32 == 0 && (BN / (MT == 2 ? 1 : 2)) % 32 == 0, "the epilogues work in 32-column chunks");
     static_assert(kSmemBytes <= 232448, "shared memory budget (227 KB per CTA)");
 };
-
-struct GemmParams {
-    void* C;
-    int64_t ldc;
-    int M, N, K;
-    int bf16;
-    int* status;
-    // fused output prune (unused by the plain kernel)
-    void* c_vals;
-    uint32_t* c_meta_ref;
-    uint32_t* c_meta_tc;
-};
-
-__device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code)
-{
-    atomicCAS(status, 0, code);
-    *abort_flag = 1;
-}
-
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& tm, int& tn)
-{
-    const int group_size = kGroupM * num_n;
-    const int group_id = t / group_size;
-    const int first_m = group_id * kGroupM;
-    const int gm = min(num_m - first_m, kGroupM);
-    const int in_group = t - group_id * group_size;
-    tm = first_m + in_group % gm;
-    tn = in_group / gm;
-}
-
-__device__ __forceinline__ uint32_t pack2(float a, float b, int bf16)
-{
-    if (bf16) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<uint32_t*>(&v);
-    }
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // 2:4 prune of four fp32 accumulators along N, as the reference's fused epilogue does
 // (compression/kernels/10.1_prune_acc.py:100-117): signed keys, >= so the lower index survives
@@ -508,7 +466,7 @@ static EncodeTiledFn encode_tiled()
     return fn;
 }
 
-static int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t inner,
+int make_map_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t inner,
                        uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
                        CUtensorMapSwizzle swz, const char* what)
 {
@@ -590,7 +548,7 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
     return check_cuda(cudaLaunchKernelEx(&lc, spmm_kernel<Cfg>, tm_a, tm_b, tm_e, g.p), "sparse GEMM launch");
 }
 
-static int* status_word_address()
+int* status_word_address()
 {
     // device address of g_status_word for the current device (looked up once per device)
     static int* cached[64] = {nullptr};

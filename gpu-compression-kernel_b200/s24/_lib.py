@@ -39,6 +39,7 @@ SIGNATURES = {
                                          ctypes.POINTER(TileCfg), _vp]),
     "s24_spmm_prune_out": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32,
                                   ctypes.POINTER(TileCfg), _vp]),
+    "s24_spmm_prune_in": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "s24_relayout_shards": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "s24_device_status": (_i32, [_vp]),
 }

@@ -312,6 +312,36 @@ def spmm_prune_out(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta
     return cv, ce, ct
 
 
+def spmm_prune_in(A: torch.Tensor, B: torch.Tensor, mode: str = "signed", tie: str = "higher",
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = prune_2_4(A) @ B with the prune + compress of the dense A done inside the GEMM kernel
+    (compression/kernels/7.8.1_prune_ws.py:112-192,609-650).  No compressed operand is materialised.
+
+    The default tie rule is the reference kernel's (strict compare: the higher index survives equal
+    keys); tie="reference" keeps the survivors of the torch function `prune_2_4` instead.
+    """
+    _require_cuda(A, B)
+    if A.dim() != 2 or B.dim() != 2 or A.shape[1] != B.shape[0]:
+        raise RuntimeError(f"shapes do not chain: A {tuple(A.shape)}, B {tuple(B.shape)}")
+    if A.dtype not in _DT or B.dtype != A.dtype:
+        raise RuntimeError(f"A and B must both be float16 or bfloat16 (got {A.dtype}, {B.dtype})")
+    M, K = A.shape
+    N = B.shape[1]
+    if M <= 0 or M % 128 != 0 or K <= 0 or K % 128 != 0 or N <= 0 or N % 8 != 0:
+        raise RuntimeError(f"needs M % 128 == 0, K % 128 == 0, N % 8 == 0 (got M={M}, N={N}, K={K})")
+    a = _row_major(A)
+    b = _row_major(B)
+    c = out if out is not None else torch.empty((M, N), dtype=A.dtype, device=A.device)
+    if (tuple(c.shape) != (M, N) or c.dtype != A.dtype or c.device != A.device or c.stride(1) != 1
+            or c.stride(0) % 8 != 0 or c.data_ptr() % 16 != 0):
+        raise RuntimeError(f"`out` must be a ({M}, {N}) {A.dtype} tensor on {A.device} with unit column stride, "
+                           "a row stride that is a multiple of 8 and 16-byte alignment")
+    with _on_device(A):
+        L.check(L.lib().s24_spmm_prune_in(_p(a), a.stride(0), _p(b), _p(c), M, N, K, b.stride(0), c.stride(0),
+                                          _DT[A.dtype], _MODE[mode], _TIE[tie], _stream(A)))
+    return c
+
+
 def relayout_shards(stage: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """stage (G, rows, nl) shard-major -> out (rows, G * nl) row-major (see s24_relayout_shards)."""
     _require_cuda(stage, out)

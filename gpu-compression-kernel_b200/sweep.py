@@ -11,6 +11,7 @@ the reference's units (dense-equivalent TFLOP/s = 2 M N K / t, GB/s = 3.125 M K 
   dense        torch.matmul of the pruned dense A (cuBLAS; stands in for the reference's dense WS kernel)
   sparse       precompressed sparse GEMM (gluon_ws_sparse.py: run_sparse_ws_matmul)
   two_kernel   prune+compress kernel then sparse GEMM (v11.1: run_2_kernel_ws_matmul)
+  fused_in     sparse GEMM that prunes + compresses the dense A inside the kernel (v7.8.1)
   fused_out    sparse GEMM with the pruning epilogue (v10.1)
   separated    sparse GEMM then prune+compress of C (v10.2)
   compress     the standalone prune+compress kernel, GB/s
@@ -143,6 +144,7 @@ def main():
             s24.spmm(v, t, B, out=C)
 
         rec["two_kernel"] = tf(timeit(two_kernel))
+        rec["fused_in"] = tf(timeit(lambda: s24.spmm_prune_in(A, B, out=C)))
         if args.vendor:
             try:
                 from torch.sparse import to_sparse_semi_structured

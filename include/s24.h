@@ -19,6 +19,7 @@
  *   s24_spmm_ref_meta    same launcher, fed the reference's metadata layout directly
  *   s24_spmm_bt          same launcher, B given transposed ((N, K) row-major)
  *   s24_spmm_prune_out   compression/kernels/10.1_prune_acc.py:88-154,359-398,624-678
+ *   s24_spmm_prune_in    compression/kernels/7.8.1_prune_ws.py:112-192,345-374,609-650
  *
  * Element types: S24_FP16 / S24_BF16, 16-bit storage, row-major matrices.
  *
@@ -207,6 +208,22 @@ S24_API int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void
                        void* C_vals, void* C_meta_ref, void* C_meta_tc,
                        int64_t M, int64_t N, int64_t K, int64_t ldb, int dtype,
                        const s24_tile_cfg* cfg, void* stream);
+
+/*
+ * Sparse GEMM that takes its left operand DENSE and 2:4-prunes + compresses it inside the
+ * kernel, C = prune_2_4(A) . B (compression/kernels/7.8.1_prune_ws.py:609-650,
+ * run_sparse_ws_matmul(A, B); in-kernel prune :112-192).  A is (M, K) with row stride lda,
+ * never modified; no compressed operand or metadata is written to memory.  mode and tie as
+ * for s24_prune_compress (the reference's kernel ranks signed values with a strict compare,
+ * i.e. S24_MODE_SIGNED with S24_TIE_HIGHER; S24_TIE_REFERENCE gives the survivors of the torch
+ * function prune_2_4 that the reference checks its kernel against).  Shape rules as for s24_spmm plus
+ * lda >= K, lda % 8 == 0.  The result is bit-identical to s24_prune_compress followed by
+ * s24_spmm on the 256 x 256 tile.  One tile shape (256 x 256 per CTA pair); every k-block of A
+ * is pruned once per 256 columns of C, so for large N the two-kernel path is the faster one.
+ */
+S24_API int s24_spmm_prune_in(const void* A, int64_t lda, const void* B, void* C,
+                      int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc,
+                      int dtype, int mode, int tie, void* stream);
 
 /*
  * Multi-GPU helper (the reference is single-GPU; no counterpart there).  When C is computed in
