@@ -18,7 +18,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "s24" / "libs24.so"
-SOURCES = ["api.cu", "prune_compress.cu", "spmm_tcgen05.cu", "spmm_prune_in.cu"]
+SOURCES = ["api.cu", "prune_compress.cu", "spmm_tcgen05.cu", "spmm_prune_in.cu", "peer.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

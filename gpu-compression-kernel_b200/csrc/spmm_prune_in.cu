@@ -425,6 +425,8 @@ extern "C" int s24_spmm_prune_in(const void* A, int64_t lda, const void* B, void
     pp.g.c_vals = nullptr;
     pp.g.c_meta_ref = nullptr;
     pp.g.c_meta_tc = nullptr;
+    pp.g.n_dst = 0;
+    for (int d = 0; d < 8; ++d) pp.g.dst[d] = nullptr;
     pp.A = static_cast<const uint16_t*>(A);
     pp.lda = lda;
     pp.tie = tie;

@@ -25,6 +25,10 @@ struct GemmParams {
     void* c_vals;
     uint32_t* c_meta_ref;
     uint32_t* c_meta_tc;
+    // scatter epilogue: the C tile goes to each of these (this GPU's buffer and peers' mappings),
+    // all with row stride ldc; unused by the other kernels
+    void* dst[8];
+    int n_dst;
 };
 
 __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code)

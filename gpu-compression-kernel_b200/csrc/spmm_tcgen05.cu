@@ -49,10 +49,16 @@ constexpr int kThreads = 320;       // producer warp, MMA warp, 8 epilogue warps
 // the bytes brought into each SM per flop by a quarter and deepens the ring in MMA time.
 // BT: B is given transposed, (N, K) row-major (activations stored (tokens, hidden)); its tiles are
 // then K-major in shared memory like A's, loaded as two 64-wide K atoms per stage.
-template <int G, int BN, int STAGES, bool PRUNE_OUT = false, int MT = 1, bool BT = false>
+// SCATTER: the epilogue stores every C tile to several destinations (this GPU's and its peers'
+// copies of a replicated result) through a shared-memory transpose that makes the stores whole lines.
+template <int G, int BN, int STAGES, bool PRUNE_OUT = false, int MT = 1, bool BT = false, bool SCATTER = false>
 struct GemmCfg {
     static constexpr bool kPruneOut = PRUNE_OUT;
     static constexpr bool kBT = BT;
+    static constexpr bool kScatter = SCATTER;
+    static constexpr int kScatterPitch = 272;                   // 256-byte row segments, padded against bank conflicts
+    static constexpr int kScatterWarpBytes = 32 * kScatterPitch; // 32 rows x 128 columns x 2 B per epilogue warp
+    static constexpr int kScatterBytes = SCATTER ? 8 * kScatterWarpBytes : 0;
     static constexpr int kG = G;
     static constexpr int kBN = BN;
     static constexpr int kMT = MT;
@@ -73,7 +79,8 @@ struct GemmCfg {
     static constexpr int kAccCols = BN * MT;                    // one accumulator set
     static constexpr int kAccStages = (kAccCols >= 256) ? 1 : 2;
     static constexpr int kECol0 = kAccStages * kAccCols;        // metadata columns follow the accumulators
-    static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kSmemBytes = STAGES * kStageBytes + kScatterBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(!SCATTER || (MT == 1 && BN == 256 && !PRUNE_OUT), "the scatter epilogue is written for 128-column warp slices");
     static_assert(kECol0 + 4 * MT * STAGES <= (int)kTmemCols, "tensor memory budget");
     static_assert(kBNCta % 8 == 0 && BN % (16 * G) == 0, "MMA N granularity");
     static_assert(BN % 32 == 0 && (BN / (MT == 2 ? 1 : 2)) % 32 == 0, "the epilogues work in 32-column chunks");
@@ -110,7 +117,8 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t smem_a = smem_base;
     const uint32_t smem_b = smem_a + STAGES * Cfg::kABytes;
     const uint32_t smem_e = smem_b + STAGES * Cfg::kBBytes;
-    const uint32_t bars = smem_e + STAGES * Cfg::kEBytes;
+    const uint32_t smem_scatter = smem_e + STAGES * Cfg::kEBytes;
+    const uint32_t bars = smem_scatter + Cfg::kScatterBytes;
     // barrier block: full[STAGES], empty[STAGES], acc_full[ACC], acc_empty[ACC], tmem slot, abort flag
     const uint32_t bar_full = bars;
     const uint32_t bar_empty = bar_full + 8 * STAGES;
@@ -292,7 +300,37 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * Cfg::kAccCols + sub * BN + chalf * CW);
             const int64_t row = (int64_t)tm * Cfg::kTileRows + (sub * G + (int)cta_rank) * kRowsPerCta + quad * 32 + lane;
             const int col0 = tn * BN + chalf * CW;
-            if constexpr (!Cfg::kPruneOut) {
+            if constexpr (Cfg::kScatter) {
+                // One load round trip for this warp's 32 rows x 128 columns, TMEM handed back at once.
+                // Each thread then parks its row segment (256 bytes) in a private slice of shared
+                // memory and hands it to the bulk-copy engine once per destination: the stores leave
+                // the SM as whole 256-byte bursts -- what a peer GPU's memory wants to see across
+                // NVLink -- and the warp does not wait for them until it needs the slice again.
+                uint32_t r[128];
+                tc_ld_32x32b_x128(tacc, r);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+                const uint32_t stg = smem_scatter + (uint32_t)(warp - 2) * (uint32_t)Cfg::kScatterWarpBytes +
+                                     (uint32_t)lane * (uint32_t)Cfg::kScatterPitch;
+                bulk_wait_read();   // the previous tile's copies have read this slice
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    st_shared_v4(stg + (uint32_t)(c * 16),
+                                 pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1]), p.bf16),
+                                 pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]), p.bf16),
+                                 pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]), p.bf16),
+                                 pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]), p.bf16));
+                fence_proxy_async_shared();
+                const int ncols = min(CW, p.N - col0);   // N % 8 == 0: a whole number of 16-byte pieces
+                if (row < p.M && ncols > 0) {
+                    const int64_t off = row * p.ldc + col0;
+                    for (int d = 0; d < p.n_dst; ++d)
+                        bulk_store(static_cast<uint16_t*>(p.dst[d]) + off, stg, (uint32_t)(ncols * 2));
+                }
+                bulk_commit();
+            } else if constexpr (!Cfg::kPruneOut) {
                 // Drain in as few round trips as possible: one tcgen05.ld per 128 (then 64, then 32)
                 // columns, convert, and hand each 8-column group to the store unit right away, so
                 // only the load round trips (not the stores) stand between the MMA warp and its
@@ -438,6 +476,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 
     // ------------------------------------------------------------ teardown
+    if constexpr (Cfg::kScatter) bulk_wait_all();   // every thread's own bulk stores have been performed
     tc_fence_before();
     __syncthreads();
     if (G == 2) cluster_sync();
@@ -565,9 +604,17 @@ int* status_word_address()
 static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                     int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, cudaStream_t stream,
                     bool prune_out = false, void* c_vals = nullptr, void* c_meta_ref = nullptr, void* c_meta_tc = nullptr,
-                    bool bt = false)
+                    bool bt = false, void* const* dsts = nullptr, int n_dst = 0)
 {
-    const char* who = prune_out ? "spmm_prune_out" : (bt ? "spmm_bt" : "spmm");
+    const char* who = prune_out ? "spmm_prune_out" : (bt ? "spmm_bt" : (dsts ? "spmm_scatter" : "spmm"));
+    if (dsts != nullptr) {
+        if (prune_out || bt) return fail(S24_ERR_UNSUPPORTED, "%s: plain row-major product only", who);
+        if (n_dst < 1 || n_dst > 8) return fail(S24_ERR_INVALID_ARG, "%s: 1 to 8 destinations (got %d)", who, n_dst);
+        for (int d = 0; d < n_dst; ++d)
+            if (dsts[d] == nullptr || !aligned(dsts[d], 16))
+                return fail(S24_ERR_INVALID_ARG, "%s: destination %d is null or not 16-byte aligned", who, d);
+        C = dsts[0];
+    }
     if (bt && prune_out) return fail(S24_ERR_UNSUPPORTED, "spmm_prune_out: transposed B is not supported");
     if (vals == nullptr || meta_tc == nullptr || B == nullptr || (!prune_out && C == nullptr) || (prune_out && c_vals == nullptr))
         return fail(S24_ERR_INVALID_ARG, "%s: null pointer", who);
@@ -606,6 +653,9 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.c_vals = c_vals;
     g.p.c_meta_ref = static_cast<uint32_t*>(c_meta_ref);
     g.p.c_meta_tc = static_cast<uint32_t*>(c_meta_tc);
+    g.p.n_dst = dsts ? n_dst : 0;
+    for (int d = 0; d < 8; ++d) g.p.dst[d] = (dsts && d < n_dst) ? dsts[d] : nullptr;
+    if (dsts != nullptr) return launch_cfg<GemmCfg<2, 256, 3, false, 1, false, true>>(g, stream);
 
     int bm = cfg ? cfg->bm : 0, bn = cfg ? cfg->bn : 0;
     // Heuristic when the caller names no tile: score = (useful fraction of the persistent waves)
@@ -666,6 +716,14 @@ extern "C" int s24_spmm_bt(const void* vals, const void* meta_tc, const void* Bt
 {
     return run_spmm(vals, meta_tc, Bt, C, M, N, K, ldbt, ldc, dtype, cfg, static_cast<cudaStream_t>(stream), false, nullptr,
                     nullptr, nullptr, true);
+}
+
+extern "C" int s24_spmm_scatter(const void* vals, const void* meta_tc, const void* B, void* const* dsts, int n_dst, int64_t M,
+                                int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype, void* stream)
+{
+    if (dsts == nullptr) return fail(S24_ERR_INVALID_ARG, "spmm_scatter: null destination list");
+    return run_spmm(vals, meta_tc, B, nullptr, M, N, K, ldb, ldc, dtype, nullptr, static_cast<cudaStream_t>(stream), false,
+                    nullptr, nullptr, nullptr, false, dsts, n_dst);
 }
 
 extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const void* B, void* C, int64_t M, int64_t N,

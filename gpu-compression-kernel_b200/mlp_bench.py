@@ -1,13 +1,13 @@
 """Multi-GPU MLP-shaped sparse GEMM: 2:4-sparse bf16 weight W (28672 x 8192, ~N(0, 0.02)) times
 activations X (8192 x 65536, ~N(0, 1)), output columns sharded over the ranks (strong scaling:
-the 65536 columns are split over 1 / 2 / 4 / 8 GPUs), with and without the NCCL all-gather that
-a replicated result needs.  Launch one process per GPU:
+the 65536 columns are split over 1 / 2 / 4 / 8 GPUs), without a replicated result, with one made
+by an NCCL all-gather, and with one made by the GEMM storing each shard into all ranks' copies.  Launch one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
         gpu-compression-kernel_b200/mlp_bench.py [--steps 10]
 
 Rank 0 prints one JSON line: aggregate dense-equivalent TFLOP/s (max-over-ranks device time)
-for the sharded result and for the replicated one.
+for the sharded result and for the two replicated ones.
 """
 from __future__ import annotations
 
@@ -76,6 +76,12 @@ def main():
         ms_rep = timed(lambda: op(X, n_total=N, replicated=True, panels=8), args.gather_steps)
         line["replicated"] = {"ms": ms_rep, "tflops": flops / ms_rep / 1e9,
                               "gathered_bytes_per_gpu": M * N * 2 * (world - 1) // world}
+        # the same replicated result with the shard stored into every rank's copy of C by the GEMM's
+        # own epilogue (peer-mapped buffers, no collective on the data path)
+        ms_fused = timed(lambda: op(X, n_total=N, replicated="fused"), args.gather_steps)
+        line["replicated_fused"] = {"ms": ms_fused, "tflops": flops / ms_fused / 1e9,
+                                    "stored_to_peers_bytes_per_gpu": M * (N // world) * 2 * (world - 1)}
+        op.close()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

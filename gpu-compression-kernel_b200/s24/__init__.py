@@ -6,4 +6,4 @@ directory; this package is what they call.
 """
 from ._lib import S24Error, lib, LIB_PATH  # noqa: F401
 from .ops import (prune, compress, prune_compress, meta_convert, meta_tc_numel, spmm,  # noqa: F401
-                  spmm_prune_out, spmm_prune_in, relayout_shards)
+                  spmm_prune_out, spmm_prune_in, spmm_scatter, relayout_shards)

@@ -14,6 +14,7 @@ MODE_SIGNED, MODE_MAGNITUDE = 0, 1
 TIE_REFERENCE, TIE_LOWER, TIE_HIGHER = 0, 1, 2
 META_LOGICAL, META_REF, META_TC = 0, 1, 2
 STATIC_SCRATCH_BYTES = 8 << 20
+PEER_HANDLE_BYTES = 64
 
 # every symbol include/s24.h declares, with (restype, argtypes)
 _vp, _i64, _i32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
@@ -40,6 +41,12 @@ SIGNATURES = {
     "s24_spmm_prune_out": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32,
                                   ctypes.POINTER(TileCfg), _vp]),
     "s24_spmm_prune_in": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
+    "s24_spmm_scatter": (_i32, [_vp, _vp, _vp, ctypes.POINTER(_vp), _i32, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "s24_peer_alloc": (_i32, [_sz, ctypes.POINTER(_vp)]),
+    "s24_peer_free": (_i32, [_vp]),
+    "s24_peer_export": (_i32, [_vp, _vp]),
+    "s24_peer_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
+    "s24_peer_close": (_i32, [_vp]),
     "s24_relayout_shards": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "s24_device_status": (_i32, [_vp]),
 }

@@ -4,7 +4,10 @@ C[:, n0:n1] = A24 . B[:, n0:n1] has no reduction across column shards, so every 
 the whole compressed A (values + tensor-core metadata), owns a contiguous range of B's and
 C's columns and runs the single-GPU kernel on it: no collective is on the data path.  NCCL
 is used only when the caller asks for a replicated result; then C is all-gathered, in row
-panels so that the gather of one panel overlaps the GEMM of the next.
+panels so that the gather of one panel overlaps the GEMM of the next.  With replicated="fused"
+there is no separate collective at all: every rank's copy of C lives in a buffer that the other
+ranks have mapped (`PeerBuffer`), and each rank's GEMM stores its column shard into all copies
+from its epilogue, so the shard crosses NVLink tile by tile while the GEMM runs.
 
 The reference project is single-GPU; this module has no counterpart there.
 """
@@ -47,6 +50,91 @@ def row_panels(m: int, panels: int, multiple: int = 128) -> List[Tuple[int, int]
     return out
 
 
+class _CudaPeerBackend:
+    """exportable device memory through the library's CUDA IPC helpers"""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+
+    def alloc(self, nbytes: int) -> int:
+        from . import ops
+        return ops.peer_alloc(nbytes, self.device)
+
+    def free(self, ptr: int) -> None:
+        from . import ops
+        ops.peer_free(ptr)
+
+    def export(self, ptr: int) -> bytes:
+        from . import ops
+        return ops.peer_export(ptr)
+
+    def open(self, handle: bytes) -> int:
+        from . import ops
+        return ops.peer_open(handle, self.device)
+
+    def close(self, ptr: int) -> None:
+        from . import ops
+        ops.peer_close(ptr)
+
+    def as_tensor(self, ptr: int, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        class _Raw:   # zero-copy view of the allocation through the CUDA array interface
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (rows * cols,), "typestr": "<i2", "data": (ptr, False),
+                                        "strides": None, "version": 3}
+        return torch.as_tensor(raw, device=self.device).view(dtype).view(rows, cols)
+
+
+class PeerBuffer:
+    """A (rows, cols) 16-bit matrix per rank, each mapped into every other rank's process.
+
+    `tensor` is this rank's copy; `ptrs[g]` is the address of rank g's copy as seen from this
+    rank (its own allocation for g == rank).  Collective over `group`: every rank constructs it
+    with the same shape.  `close()` is collective too (mappings are closed everywhere before any
+    owner frees).  `backend` supplies alloc / export / open / close / free / as_tensor; the default
+    uses CUDA IPC, tests on CPU ranks pass a shared-file stand-in.
+    """
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, device: torch.device, group=None, backend=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.backend = backend or _CudaPeerBackend(device)
+        self.rows, self.cols, self.dtype = rows, cols, dtype
+        self._own = self.backend.alloc(rows * cols * 2)
+        handle = self.backend.export(self._own)
+        if len(handle) != self.HANDLE_BYTES:
+            raise RuntimeError(f"peer handle of {len(handle)} bytes, expected {self.HANDLE_BYTES}")
+        comm_dev = device if dist.get_backend(group) == "nccl" else torch.device("cpu")
+        mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(comm_dev)
+        everyone = torch.empty(self.world * self.HANDLE_BYTES, dtype=torch.uint8, device=comm_dev)   # rank-major
+        dist.all_gather_into_tensor(everyone, mine, group=group)
+        everyone = everyone.cpu().view(self.world, self.HANDLE_BYTES)
+        self.ptrs: List[int] = []
+        for g in range(self.world):
+            self.ptrs.append(self._own if g == self.rank else self.backend.open(bytes(everyone[g].tolist())))
+        self.tensor = self.backend.as_tensor(self._own, rows, cols, dtype)
+        self._open = True
+
+    def close(self) -> None:
+        if not self._open:
+            return
+        self._open = False
+        self.tensor = None
+        for g, ptr in enumerate(self.ptrs):
+            if g != self.rank:
+                self.backend.close(ptr)
+        dist.barrier(group=self.group)      # nobody still maps a buffer that is about to be freed
+        self.backend.free(self._own)
+
+
+def _default_scatter(vals, meta_tc, B, dst_ptrs, ldc):
+    from . import ops
+    ops.spmm_scatter(vals, meta_tc, B, dst_ptrs, ldc)
+
+
 def _default_spmm(vals, meta_tc, B, out=None):
     from . import ops
     return ops.spmm(vals, meta_tc, B, meta_layout="tc", out=out)
@@ -60,9 +148,12 @@ class NShardedSpmm:
     group          : torch.distributed process group (default: the world group)
     spmm_fn        : the single-device product, `spmm_fn(vals, meta_tc, B_shard, out=...)`;
                      defaults to the tcgen05 kernel.  Tests on CPU ranks pass a stand-in.
+    scatter_fn     : the product stored to several destinations (replicated="fused");
+                     defaults to `s24_spmm_scatter`.  peer_backend: see `PeerBuffer`.
     """
 
-    def __init__(self, vals: torch.Tensor, meta_tc: torch.Tensor, group=None, spmm_fn: Optional[Callable] = None):
+    def __init__(self, vals: torch.Tensor, meta_tc: torch.Tensor, group=None, spmm_fn: Optional[Callable] = None,
+                 scatter_fn: Optional[Callable] = None, peer_backend=None):
         self.vals = vals
         self.meta_tc = meta_tc
         self.group = group
@@ -72,14 +163,21 @@ class NShardedSpmm:
         self.M = vals.shape[0]
         self.K = vals.shape[1] * 2
         self._comm_stream = None
+        self.scatter_fn = scatter_fn or _default_scatter   # scatter_fn(vals, meta_tc, B_shard, dst_ptrs, ldc)
+        self.peer_backend = peer_backend
+        self._peer: Optional[PeerBuffer] = None
+        self._fence_flag: Optional[torch.Tensor] = None
 
     def local_columns(self, n_total: int) -> Tuple[int, int]:
         return shard_bounds(n_total, self.world, self.rank)
 
-    def __call__(self, B_shard: torch.Tensor, n_total: Optional[int] = None, replicated: bool = False,
+    def __call__(self, B_shard: torch.Tensor, n_total: Optional[int] = None, replicated=False,
                  panels: int = 4) -> torch.Tensor:
         """B_shard: this rank's (K, N_local) columns of B.  Returns the local (M, N_local)
-        shard of C, or with replicated=True the full (M, n_total) C on every rank."""
+        shard of C, or with replicated=True the full (M, n_total) C on every rank (all-gather).
+        replicated="fused" gives the same result without a collective on the data path: the GEMM
+        itself stores each shard into every rank's copy of C.  That copy is a buffer owned by this
+        object and is returned again (overwritten) by the next fused call of the same shape."""
         if B_shard.shape[0] != self.K:
             raise RuntimeError(f"B shard has {B_shard.shape[0]} rows, expected K={self.K}")
         n_local = B_shard.shape[1]
@@ -90,7 +188,40 @@ class NShardedSpmm:
         if n_local * self.world != n_total:
             raise RuntimeError("replicated output needs equal column shards on every rank "
                                f"(N_local={n_local}, world={self.world}, N={n_total})")
+        if replicated == "fused":
+            return self._fused(B_shard, n_total)
         return self._gathered(B_shard, n_total, panels)
+
+    def _fence(self, device: torch.device) -> None:
+        """order the ranks on the current stream without blocking the host: a one-element all-reduce"""
+        if self._fence_flag is None or self._fence_flag.device != device:
+            self._fence_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.all_reduce(self._fence_flag, group=self.group)
+
+    def _fused(self, B_shard: torch.Tensor, n_total: int) -> torch.Tensor:
+        M, G, nl = self.M, self.world, B_shard.shape[1]
+        dev = B_shard.device
+        if self._peer is not None and (self._peer.rows, self._peer.cols) != (M, n_total):
+            self._peer.close()
+            self._peer = None
+        if self._peer is None:
+            self._peer = PeerBuffer(M, n_total, self.vals.dtype, dev, group=self.group, backend=self.peer_backend)
+        buf = self._peer
+        self._fence(dev)          # every rank is done reading the previous result
+        col0 = self.rank * nl
+        # start with this rank's own copy and go round the ring, so that at any moment the ranks
+        # store to different destinations
+        order = [(self.rank + i) % G for i in range(G)]
+        dsts = [buf.ptrs[g] + 2 * col0 for g in order]
+        self.scatter_fn(self.vals, self.meta_tc, B_shard, dsts, n_total)
+        self._fence(dev)          # every rank's shard has landed in every copy
+        return buf.tensor
+
+    def close(self) -> None:
+        """release the peer-mapped result buffer (collective)"""
+        if self._peer is not None:
+            self._peer.close()
+            self._peer = None
 
     def _gathered(self, B_shard: torch.Tensor, n_total: int, panels: int) -> torch.Tensor:
         M, G, nl = self.M, self.world, B_shard.shape[1]

@@ -342,6 +342,55 @@ def spmm_prune_in(A: torch.Tensor, B: torch.Tensor, mode: str = "signed", tie: s
     return c
 
 
+def spmm_scatter(vals: torch.Tensor, meta_tc: torch.Tensor, B: torch.Tensor, dst_ptrs, ldc: int) -> None:
+    """C = A24 @ B stored to every address in `dst_ptrs` (1..8 device addresses of element (0, 0) of
+    this product inside a destination with row stride `ldc`; this GPU's memory or peers' buffers
+    opened with `peer_open`).  See s24_spmm_scatter; the caller orders the ranks afterwards."""
+    _require_cuda(vals, meta_tc, B)
+    M, N, K = _check_gemm(vals, B)
+    dst_ptrs = [int(x) for x in dst_ptrs]
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise RuntimeError(f"1 to 8 destinations (got {len(dst_ptrs)})")
+    v = vals.contiguous()
+    b = _row_major(B)
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    with _on_device(vals):
+        L.check(L.lib().s24_spmm_scatter(_p(v), _p(meta_tc), _p(b), arr, len(dst_ptrs), M, N, K, b.stride(0), int(ldc),
+                                         _DT[vals.dtype], _stream(vals)))
+
+
+def peer_alloc(nbytes: int, device: torch.device) -> int:
+    """exportable device memory on `device` (cudaMalloc; set-up code only)"""
+    out = ctypes.c_void_p()
+    with torch.cuda.device(device):
+        L.check(L.lib().s24_peer_alloc(int(nbytes), ctypes.byref(out)))
+    return int(out.value)
+
+
+def peer_free(ptr: int) -> None:
+    L.check(L.lib().s24_peer_free(ctypes.c_void_p(ptr)))
+
+
+def peer_export(ptr: int) -> bytes:
+    buf = ctypes.create_string_buffer(L.PEER_HANDLE_BYTES)
+    L.check(L.lib().s24_peer_export(ctypes.c_void_p(ptr), buf))
+    return buf.raw
+
+
+def peer_open(handle: bytes, device: torch.device) -> int:
+    """map another process's exported buffer; `device` is the GPU whose kernels will store to it"""
+    if len(handle) != L.PEER_HANDLE_BYTES:
+        raise RuntimeError(f"a peer handle has {L.PEER_HANDLE_BYTES} bytes (got {len(handle)})")
+    out = ctypes.c_void_p()
+    with torch.cuda.device(device):
+        L.check(L.lib().s24_peer_open(ctypes.create_string_buffer(handle, L.PEER_HANDLE_BYTES), ctypes.byref(out)))
+    return int(out.value)
+
+
+def peer_close(ptr: int) -> None:
+    L.check(L.lib().s24_peer_close(ctypes.c_void_p(ptr)))
+
+
 def relayout_shards(stage: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """stage (G, rows, nl) shard-major -> out (rows, G * nl) row-major (see s24_relayout_shards)."""
     _require_cuda(stage, out)

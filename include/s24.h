@@ -226,6 +226,38 @@ S24_API int s24_spmm_prune_in(const void* A, int64_t lda, const void* B, void* C
                       int dtype, int mode, int tie, void* stream);
 
 /*
+ * Multi-GPU: replicated result without a separate all-gather (the reference is single-GPU; no
+ * counterpart there).  s24_spmm_scatter is s24_spmm whose epilogue stores every tile of C to
+ * n_dst (1..8) destinations instead of one: dsts[d] points at element (0, 0) of this call's
+ * (M, N) block inside destination d, all destinations share the row stride ldc.  With C
+ * (M, N_total) replicated over G GPUs and the columns of B sharded, rank r passes, for every
+ * rank g, the address of column r * N/G of g's copy of C as mapped into r's address space
+ * (s24_peer_open); the shard then crosses NVLink tile by tile while the GEMM runs, as whole
+ * 256-byte row segments.  Only stores go to peer memory.  The caller orders the ranks (a barrier
+ * or any collective on the stream) before C is read and before the next call overwrites it.
+ * 256 x 256 tile; shape rules as for s24_spmm.
+ */
+S24_API int s24_spmm_scatter(const void* vals, const void* meta_tc, const void* B,
+                     void* const* dsts, int n_dst,
+                     int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc,
+                     int dtype, void* stream);
+
+/*
+ * Buffers for the above (no counterpart in the reference).  s24_peer_alloc / s24_peer_free:
+ * device memory of the current device that can be exported (plain cudaMalloc / cudaFree: they
+ * synchronise; set-up code only).  s24_peer_export writes an opaque S24_PEER_HANDLE_BYTES-byte
+ * handle that another process on the same box passes to s24_peer_open, with its own device
+ * current, to get an address its kernels can store to; s24_peer_close unmaps it.  A buffer must
+ * be closed by every opener before its owner frees it.
+ */
+#define S24_PEER_HANDLE_BYTES 64
+S24_API int s24_peer_alloc(size_t bytes, void** ptr);
+S24_API int s24_peer_free(void* ptr);
+S24_API int s24_peer_export(const void* ptr, void* handle);
+S24_API int s24_peer_open(const void* handle, void** ptr);
+S24_API int s24_peer_close(void* ptr);
+
+/*
  * Multi-GPU helper (the reference is single-GPU; no counterpart there).  When C is computed in
  * column shards, one per rank, an all-gather delivers them shard-major: stage is
  * (shards, rows, shard_cols) contiguous, 16-bit elements.  This writes the row-major matrix

@@ -27,7 +27,8 @@ def test_header_declares_the_expected_entry_points():
     names = declared_symbols()
     for want in ("s24_version", "s24_last_error", "s24_prune", "s24_compress", "s24_prune_compress",
                  "s24_meta_tc_bytes", "s24_meta_convert", "s24_spmm", "s24_spmm_ref_meta", "s24_spmm_ref_meta_noalloc", "s24_spmm_prune_out",
-                 "s24_device_status", "s24_relayout_shards", "s24_spmm_bt", "s24_spmm_prune_in"):
+                 "s24_device_status", "s24_relayout_shards", "s24_spmm_bt", "s24_spmm_prune_in", "s24_spmm_scatter",
+                 "s24_peer_alloc", "s24_peer_free", "s24_peer_export", "s24_peer_open", "s24_peer_close"):
         assert want in names
 
 

@@ -1,5 +1,6 @@
-"""N-sharded sparse GEMM on two GPUs (one process per GPU, NCCL): local shards and the
-all-gathered replicated result against a single-GPU product.  Skipped on a one-GPU box."""
+"""N-sharded sparse GEMM on two GPUs (one process per GPU, NCCL): local shards, the all-gathered
+replicated result and the one stored into peer-mapped buffers by the GEMM itself, against a
+single-GPU product.  Skipped on a one-GPU box."""
 import os
 import subprocess
 import sys
@@ -37,6 +38,18 @@ torch.cuda.synchronize()
 torch.testing.assert_close(C_full.float(), ref, rtol=1e-2, atol=1e-2 + 8e-3 * float(ref.abs().max()))
 single = s24.spmm(vals, tc, B)
 assert torch.equal(C_full, single), "gathered result differs from the single-GPU product"
+# replicated result without a collective on the data path: each rank's GEMM stores its shard into
+# every rank's peer-mapped copy of C; bit-identical to the single-GPU product on the same tile
+want = s24.spmm(vals, tc, B, manual_config={{"BM": 256, "BN": 256}})
+for it in range(3):
+    Bi = B if it == 0 else torch.roll(B, it, dims=0)
+    wi = want if it == 0 else s24.spmm(vals, tc, Bi, manual_config={{"BM": 256, "BN": 256}})
+    C_fused = op(Bi[:, n0:n1].contiguous(), n_total=N, replicated="fused")
+    torch.cuda.synchronize()
+    assert torch.equal(C_fused, wi), f"fused replicated result differs (iteration {{it}})"
+from s24 import _lib
+assert _lib.lib().s24_device_status(None) == 0, _lib.last_error()
+op.close()
 dist.barrier()
 dist.destroy_process_group()
 print("rank", rank, "ok")

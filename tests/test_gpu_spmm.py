@@ -231,3 +231,28 @@ def test_transposed_b_is_used_in_place(mods, M, N, K, dtype, cfg):
     E = torch.from_numpy(e).to(DEV)
     C_p = s24.spmm(v, E, Xp[:, :K].t(), meta_layout="ref", manual_config=cfg)
     assert torch.equal(C_p, C_n)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (384, 200, 512), (1024, 1032, 1024), (128, 8, 128)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_scatter_epilogue_writes_every_destination(mods, M, N, K, dtype):
+    """s24_spmm_scatter on one GPU: three destinations (two blocks inside one wide buffer, one
+    separate tensor) all receive the product, bit-identical to the plain kernel on the same tile,
+    and nothing around the blocks is touched."""
+    s24 = mods["s24"]
+    A, B, ap, vals, ml, e = _prepare(M, K, N, dtype, 900 + M + N + K)
+    tc = torch.from_numpy(oracle.meta_tc(ml, K).view(np.int32)).to(DEV)
+    v, Bd = from_bits(vals, dtype, DEV), B.to(DEV)
+    want = s24.spmm(v, tc, Bd, manual_config={"BM": 256, "BN": 256})
+    ldc = 2 * N + 24
+    wide = torch.full((M + 1, ldc), 3.0, dtype=dtype, device=DEV)
+    other = torch.full((M, ldc), 5.0, dtype=dtype, device=DEV)
+    dsts = [wide.data_ptr() + 2 * 8, wide.data_ptr() + 2 * (N + 16), other.data_ptr()]
+    s24.spmm_scatter(v, tc, Bd, dsts, ldc)
+    _status_ok(s24)
+    assert torch.equal(wide[:M, 8:8 + N], want) and torch.equal(wide[:M, N + 16:2 * N + 16], want)
+    assert torch.equal(other[:, :N], want)
+    assert bool((wide[:, :8] == 3.0).all()) and bool((wide[:, 8 + N:N + 16] == 3.0).all())
+    assert bool((wide[:, 2 * N + 16:] == 3.0).all()) and bool((wide[M] == 3.0).all())
+    assert bool((other[:, N:] == 5.0).all())
+    _check(want, _reference(ap, B, dtype))

@@ -99,3 +99,92 @@ def test_failing_rank_is_an_error_not_a_hang(tmp_path):
     world = 2
     with pytest.raises(Exception):
         mp.spawn(_worker, args=(world, _free_port(), 1, str(tmp_path)), nprocs=world, join=True)
+
+
+# ---------------------------------------------------------------- replicated="fused" on CPU ranks
+
+_KEY = 1 << 40   # fake device addresses: key * 2^40 + byte offset
+
+
+class _FileBackend:
+    """Stand-in for the CUDA IPC helpers: each "allocation" is a file mapped shared, so a rank's
+    stores into a peer's buffer really land in the peer process."""
+
+    def __init__(self, directory, rank):
+        self.dir, self.rank, self.maps, self.n = directory, rank, {}, 0
+
+    def _map(self, name, nbytes):
+        key = len(self.maps) + 1
+        self.maps[key] = torch.from_file(os.path.join(self.dir, name), shared=True, size=nbytes // 2, dtype=torch.int16)
+        return key * _KEY
+
+    def alloc(self, nbytes):
+        self.n += 1
+        name = f"r{self.rank}_{self.n}"
+        with open(os.path.join(self.dir, name), "wb") as f:
+            f.truncate(nbytes)
+        ptr = self._map(name, nbytes)
+        self.names = getattr(self, "names", {})
+        self.names[ptr] = (name, nbytes)
+        return ptr
+
+    def export(self, ptr):
+        name, nbytes = self.names[ptr]
+        return f"{name}:{nbytes}".encode().ljust(64, b"\0")
+
+    def open(self, handle):
+        name, nbytes = handle.rstrip(b"\0").decode().split(":")
+        return self._map(name, int(nbytes))
+
+    def close(self, ptr):
+        self.maps.pop(ptr // _KEY)
+
+    def free(self, ptr):
+        self.maps.pop(ptr // _KEY)
+
+    def as_tensor(self, ptr, rows, cols, dtype):
+        return self.maps[ptr // _KEY].view(dtype).view(rows, cols)
+
+
+def _fused_worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=30))
+    try:
+        backend = _FileBackend(result_dir, rank)
+
+        def fake_scatter(vals, meta_tc, B, dst_ptrs, ldc):
+            C = (vals.float() @ B.float()).to(vals.dtype)
+            for ptr in dst_ptrs:
+                key, off = divmod(ptr, _KEY)
+                flat = backend.maps[key].view(vals.dtype)
+                rows = flat.numel() // ldc
+                col0 = (off // 2) % ldc
+                assert off // 2 < ldc                      # the offset is a column of row 0
+                flat.view(rows, ldc)[:, col0:col0 + B.shape[1]] = C
+
+        torch.manual_seed(11)
+        M, K, N = 256, 128, 32 * world
+        A = torch.randn(M, K).to(torch.bfloat16)
+        op = NShardedSpmm(A, torch.zeros(1, dtype=torch.int32), scatter_fn=fake_scatter, peer_backend=backend)
+        op.K = K
+        n0, n1 = op.local_columns(N)
+        for it in range(3):                                # the result buffer is reused call after call
+            B = torch.randn(K, N).to(torch.bfloat16)
+            want = (A.float() @ B.float()).to(torch.bfloat16)
+            C = op(B[:, n0:n1].contiguous(), n_total=N, replicated="fused")
+            assert C.shape == (M, N) and C.dtype == torch.bfloat16
+            assert torch.equal(C, want), f"iteration {it}"
+        assert len(op._peer.ptrs) == world and op._peer.ptrs[rank] == op._peer._own
+        op.close()
+        assert op._peer is None and not backend.maps       # every mapping released
+        with open(os.path.join(result_dir, f"fused_ok_{rank}"), "w") as f:
+            f.write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_fused_replicated_result_through_peer_buffers(tmp_path, world):
+    mp.spawn(_fused_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"fused_ok_{r}").exists() for r in range(world))
