@@ -9,6 +9,8 @@ There is no fallback: CPU tensors or a missing libs24.so raise.
 from __future__ import annotations
 
 import ctypes
+import os
+import sys
 from typing import Optional, Tuple
 
 import torch
@@ -24,22 +26,33 @@ def _stream(t: torch.Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
+# S24_NVTX=1 wraps every library call in an NVTX range named after the calling front-end function,
+# the way the reference brackets its launches for Nsight (compression/dev/9.4_profile_ws.py:48-53)
+_NVTX = os.environ.get("S24_NVTX", "0") not in ("", "0")
+
+
 class _on_device:
     """`with _on_device(t):` makes t's device current for the library call; a no-op (and much
     cheaper than torch.cuda.device) when it already is, which is the common case"""
-    __slots__ = ("idx", "prev")
+    __slots__ = ("idx", "prev", "ranged")
 
     def __init__(self, t: torch.Tensor):
         self.idx = t.device.index
         self.prev = None
+        self.ranged = False
 
     def __enter__(self):
         cur = torch.cuda.current_device()
         if self.idx is not None and cur != self.idx:
             self.prev = cur
             torch.cuda.set_device(self.idx)
+        if _NVTX:
+            torch.cuda.nvtx.range_push("s24." + sys._getframe(1).f_code.co_name)
+            self.ranged = True
 
     def __exit__(self, *exc):
+        if self.ranged:
+            torch.cuda.nvtx.range_pop()
         if self.prev is not None:
             torch.cuda.set_device(self.prev)
         return False

@@ -4,6 +4,7 @@ compression/dev/8.11.1_benchmark_pruning.py for prune+compress,
 compression/dev/8.10_benchmark_post_compression.py for the fused-output lines).
 
     python gpu-compression-kernel_b200/sweep.py [--n 8192] [--dtype fp16|bf16] [--quick] [--out results.jsonl]
+    python gpu-compression-kernel_b200/sweep.py --table results.jsonl        # markdown table, no GPU needed
 
 For every (M, K) of the reference's 13 x 13 grid (N fixed) it appends one JSON line with, in
 the reference's units (dense-equivalent TFLOP/s = 2 M N K / t, GB/s = 3.125 M K / t):
@@ -81,6 +82,30 @@ def timeit(fn, target_ms=30.0):
     return a.elapsed_time(b) / n
 
 
+def print_table(path: str) -> int:
+    """render a results file of this script as a markdown table (no GPU needed)"""
+    recs = {}
+    for line in Path(path).read_text().splitlines():
+        try:
+            d = json.loads(line)
+            recs[(d["M"], d["K"])] = d          # a re-measured shape replaces its earlier line
+        except Exception:
+            continue
+    if not recs:
+        print(f"no records in {path}", file=sys.stderr)
+        return 1
+    cols = [c for c in ("dense", "sparse", "sparse_ref_meta", "two_kernel", "fused_in", "fused_out", "separated",
+                        "vendor_sparse", "vendor_two_step", "compress_gbs") if any(c in d for d in recs.values())]
+    print("| M | K | " + " | ".join(cols) + " |")
+    print("|---|---|" + "---|" * len(cols))
+    for (m, k) in sorted(recs, key=lambda mk: (-mk[0] * mk[1], -mk[0])):
+        d = recs[(m, k)]
+        print(f"| {m} | {k} | " + " | ".join(f"{d[c]:.0f}" if c in d else "-" for c in cols) + " |")
+    means = {c: sum(d[c] for d in recs.values() if c in d) / max(1, sum(1 for d in recs.values() if c in d)) for c in cols}
+    print("| mean | | " + " | ".join(f"{means[c]:.0f}" for c in cols) + " |")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--n", type=int, default=8192)
@@ -93,7 +118,11 @@ def main():
                     help="also time torch's semi-structured sparse matmul (cuSPARSELt / CUTLASS behind "
                          "torch.sparse.to_sparse_semi_structured), the stand-in for the reference's torchao line")
     ap.add_argument("--max-elems", type=float, default=2.5e9, help="skip shapes whose M*K exceeds this")
+    ap.add_argument("--table", metavar="RESULTS.jsonl", default=None,
+                    help="print a results file as a markdown table (TFLOP/s; last column GB/s) and exit")
     args = ap.parse_args()
+    if args.table:
+        return print_table(args.table)
     global USE_GRAPH
     USE_GRAPH = not args.eager
     dtype = torch.float16 if args.dtype == "fp16" else torch.bfloat16

@@ -244,3 +244,35 @@ def test_relayout_of_gathered_column_shards(mods):
     s24.relayout_shards(stage, out)
     assert torch.equal(out, stage.permute(1, 0, 2).reshape(rows, G * nl))
     assert float(wide[:, G * nl:].abs().max()) == 0
+
+
+def test_property_random_shapes_bit_exact(mods):
+    """hypothesis-driven: random (M % 32 == 0, K % 64 == 0) shapes, dtypes, modes, tie rules and
+    value distributions (plain randn, heavy ties, tiny magnitudes with denormals); values and both
+    metadata layouts must equal the oracle's bit for bit"""
+    from hypothesis import given, settings, strategies as st, HealthCheck
+    s24 = mods["s24"]
+
+    @settings(max_examples=40, deadline=None, derandomize=True, suppress_health_check=list(HealthCheck))
+    @given(m=st.integers(1, 16), k=st.integers(1, 12), seed=st.integers(0, 2 ** 20),
+           dtype=st.sampled_from([torch.float16, torch.bfloat16]), mode=st.sampled_from(["signed", "magnitude"]),
+           tie=st.sampled_from(["reference", "lower", "higher"]), kind=st.sampled_from(["randn", "ties", "tiny"]))
+    def run(m, k, seed, dtype, mode, tie, kind):
+        M, K = 32 * m, 64 * k
+        if kind == "randn":
+            A = randn((M, K), dtype, seed)
+        elif kind == "ties":
+            A = tie_heavy((M, K), dtype, seed)
+        else:
+            A = randn((M, K), dtype, seed, scale=3e-7 if dtype == torch.float16 else 1e-39)
+        want_p = oracle.prune(bits(A), ODT[dtype], MODE[mode], TIE[tie])
+        want_v, want_ml, want_e = oracle.compress(want_p, ODT[dtype])
+        with_tc = M % 128 == 0 and K % 128 == 0
+        v, e, tc = s24.prune_compress(A.to(DEV), mode=mode, tie=tie, want_ref=True, want_tc=with_tc)
+        assert np.array_equal(bits(v), want_v)
+        assert np.array_equal(e.cpu().numpy(), want_e)
+        if with_tc:
+            assert np.array_equal(tc.cpu().numpy().view(np.uint32), oracle.meta_tc(want_ml, K))
+        assert np.array_equal(bits(s24.prune(A.to(DEV), mode=mode, tie=tie)), want_p)
+
+    run()
