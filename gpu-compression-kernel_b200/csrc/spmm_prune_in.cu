@@ -8,23 +8,25 @@
 // load and the wgmma of the same warps; here it runs in warps of its own, beside an MMA that
 // is asynchronous and takes its metadata from tensor memory:
 //
-//   * warp 0: TMA producer for B only (its half of the 128 x 256 B tile per k-block);
+//   * warp 0: TMA producer for B only, a 4-stage ring of 64 k-rows x 2 x 120 columns per CTA;
 //   * warps 6-21: prune warps.  Each owns 16 rows x 64 columns of this CTA's 128-row slab.  Per
 //     k-block each lane reads 2 x 32 bytes of dense A straight from global memory (the next
 //     k-block's loads are issued before the current one is ranked), ranks them with the same
 //     packed half2 arithmetic as the standalone prune+compress kernel and stores
-//       - the surviving values into the A operand stage in the 128-byte-swizzled K-major form
-//         a TMA load of precompressed values would have produced, and
+//       - the surviving values into the A operand stage (a 4-stage ring of its own) in the
+//         128-byte-swizzled K-major form a TMA load of precompressed values would have produced,
 //       - the metadata words into the 2 KB record that tcgen05.cp moves into tensor memory,
 //     then fences the stores towards the asynchronous proxy and arrives on the leader CTA's
 //     "A ready" barrier;
 //   * warp 1: MMA issuer (leader CTA of the pair): waits for B (bytes) and A (prune warps of
-//     both CTAs), copies the metadata record into tensor memory, issues four K = 32 sparse MMAs,
-//     commits to both CTAs' "empty" barriers;
+//     both CTAs), copies the metadata record into tensor memory, issues four K = 32 sparse MMAs
+//     per column sub-tile, commits to both CTAs' "A free" and "B empty" barriers;
 //   * warps 2-5: epilogue, one warp per tensor-memory lane quadrant.
-// A CTA pair computes a 256 x 256 tile; dense A never passes through shared memory.
-// Every k-block of A is pruned once per column tile of C (N / 256 times in all), which is what
-// bounds this variant at large N; at N <= 256 it reads A once and saves the round trip of the
+// A CTA pair computes a 256 x 480 tile as two 240-column sub-tiles that share every pruned A
+// stage (accumulators and metadata fill 496 of the 512 tensor-memory columns); dense A never passes
+// through shared memory.  Every k-block of A is ranked once per 480 columns of C, which is what
+// bounds this variant at large N (the ranking keeps the ALU pipe busier than the MMAs keep the
+// tensor pipe); at N <= 480 it reads and ranks A once and saves the round trip of the
 // compressed operand through memory.
 // All barrier waits are bounded (status codes 1-4 as in the plain kernel, 5 = prune warp waiting
 // for a free stage, 6 = MMA warp waiting for pruned A).
@@ -39,22 +41,28 @@ using namespace ptx;
 
 namespace pin {
 constexpr int kG = 2;
-constexpr int kBN = 256;
-constexpr int kBNCta = kBN / kG;
-constexpr int kStages = 4;
+constexpr int kNT = 2;                            // column sub-tiles per tile, sharing each A stage
+constexpr int kBNSub = 240;                       // one MMA's N (a multiple of 16)
+constexpr int kBN = kNT * kBNSub;                 // tile columns
+constexpr int kBNCta = kBNSub / kG;               // B columns per CTA and sub-tile
+constexpr int kAStages = 4;                       // pruned A: stages of one k-block (128)
+constexpr int kBStages = 4;                       // B: stages of half a k-block, so that four loads are in flight
+constexpr int kBStageK = kBlockK / 2;
 constexpr int kABytes = kRowsPerCta * 128;        // 128 rows x 64 kept values x 2 B
-constexpr int kBAtomBytes = kBlockK * 128;        // 128 k-rows x 64 columns x 2 B
-constexpr int kBAtoms = kBNCta / 64;
-constexpr int kBBytes = kBAtoms * kBAtomBytes;
+constexpr int kBAtomBytes = kBStageK * 128;       // 64 k-rows x 64 columns x 2 B
+constexpr int kBAtoms = (kBNCta + 63) / 64;       // whole 64-column atoms per sub-tile (the last one partly used)
+constexpr int kBSubBytes = kBAtoms * kBAtomBytes;
+constexpr int kBBytes = kNT * kBSubBytes;
 constexpr int kEBytes = 2048;
-constexpr int kECol0 = kBN;                       // metadata columns follow the accumulator
+constexpr int kECol0 = kBN;                       // metadata columns follow the accumulators
 constexpr int kEpiWarps = 4;
 constexpr int kPruneWarps = 16;                   // 16 rows x 64 columns of the k-block each
 constexpr int kFirstPruneWarp = 2 + kEpiWarps;
 constexpr int kThreads = 32 * (2 + kEpiWarps + kPruneWarps);
-constexpr int kSmemBytes = kStages * (kABytes + kBBytes + kEBytes) + 1024 + 256;
-static_assert(kECol0 + 4 * kStages <= (int)kTmemCols, "tensor memory budget");
+constexpr int kSmemBytes = kAStages * (kABytes + kEBytes) + kBStages * kBBytes + 1024 + 256;
+static_assert(kECol0 + 4 * kAStages <= (int)kTmemCols, "tensor memory budget");
 static_assert(kSmemBytes <= 232448, "shared memory budget");
+static_assert(kBN % 32 == 0 && kBNSub % 16 == 0, "the epilogue walks the two adjacent accumulators in 32-column chunks");
 }  // namespace pin
 
 struct PruneInParams {
@@ -70,19 +78,20 @@ __global__ void __launch_bounds__(pin::kThreads, 1)
 spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInParams pp)
 {
     using namespace pin;
-    constexpr int G = kG, STAGES = kStages;
+    constexpr int G = kG;
     const GemmParams& p = pp.g;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t smem_a = smem_base;
-    const uint32_t smem_b = smem_a + STAGES * kABytes;
-    const uint32_t smem_e = smem_b + STAGES * kBBytes;
-    const uint32_t bars = smem_e + STAGES * kEBytes;
-    const uint32_t bar_full = bars;                       // B bytes have landed (leader's barrier counts both CTAs)
-    const uint32_t bar_empty = bar_full + 8 * STAGES;     // the MMAs that read the stage have completed
-    const uint32_t bar_a_ready = bar_empty + 8 * STAGES;  // every prune warp of both CTAs has filled the stage
-    const uint32_t bar_acc_full = bar_a_ready + 8 * STAGES;
+    const uint32_t smem_b = smem_a + kAStages * kABytes;
+    const uint32_t smem_e = smem_b + kBStages * kBBytes;
+    const uint32_t bars = smem_e + kAStages * kEBytes;
+    const uint32_t bar_b_full = bars;                         // B bytes have landed (leader's barrier counts both CTAs)
+    const uint32_t bar_b_empty = bar_b_full + 8 * kBStages;   // the MMAs that read the B stage have completed
+    const uint32_t bar_a_ready = bar_b_empty + 8 * kBStages;  // every prune warp of both CTAs has filled the A stage
+    const uint32_t bar_a_free = bar_a_ready + 8 * kAStages;   // the MMAs that read the A stage have completed
+    const uint32_t bar_acc_full = bar_a_free + 8 * kAStages;
     const uint32_t bar_acc_empty = bar_acc_full + 8;
     const uint32_t tmem_slot = bar_acc_empty + 8;
     const uint32_t abort_addr = tmem_slot + 8;
@@ -104,10 +113,13 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
     const int kblocks = p.K / kBlockK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 1);
+        for (int s = 0; s < kBStages; ++s) {
+            mbar_init(bar_b_full + 8 * s, 1);
+            mbar_init(bar_b_empty + 8 * s, 1);
+        }
+        for (int s = 0; s < kAStages; ++s) {
             mbar_init(bar_a_ready + 8 * s, kPruneWarps * G);
+            mbar_init(bar_a_free + 8 * s, 1);
         }
         mbar_init(bar_acc_full, 1);
         mbar_init(bar_acc_empty, kEpiWarps * G);
@@ -132,58 +144,78 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
             for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
                 int tm, tn;
                 tile_coords(t, num_m, num_n, tm, tn);
-                const int col0 = tn * kBN + (int)cta_rank * kBNCta;
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u)) {
+                const int nsub = (tn * kBN + kBNSub < p.N) ? kNT : 1;   // the last tile may have one sub-tile only
+                for (int kh = 0; kh < 2 * kblocks; ++kh) {   // half k-blocks
+                    if (!mbar_wait(bar_b_empty + 8 * s, phase ^ 1u)) {
                         report_timeout(p.status, abort_flag, 1);
                         break;
                     }
-                    const uint32_t full = mapa(bar_full + 8 * s, 0);   // the leader's barrier
-                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * kBBytes));
-                    const uint32_t b_dst = smem_b + s * kBBytes;
+                    const uint32_t full = mapa(bar_b_full + 8 * s, 0);   // the leader's barrier
+                    if (leader) mbar_arrive_expect_tx(bar_b_full + 8 * s, (uint32_t)(G * nsub * kBSubBytes));
+                    for (int n = 0; n < nsub; ++n) {
+                        const int col0 = tn * kBN + n * kBNSub + (int)cta_rank * kBNCta;
+                        const uint32_t b_dst = smem_b + s * kBBytes + n * kBSubBytes;
 #pragma unroll
-                    for (int i = 0; i < kBAtoms; ++i)
-                        tma_load_2d_pair(b_dst + i * kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                        for (int i = 0; i < kBAtoms; ++i)
+                            tma_load_2d_pair(b_dst + i * kBAtomBytes, &tm_b, col0 + 64 * i, kh * kBStageK, full);
+                    }
+                    if (++s == kBStages) { s = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (leader && elect_one()) {
-            const uint32_t idesc = make_idesc_sp_f16(p.bf16, kTileRows, kBN, 1);
-            int s = 0;
-            uint32_t phase = 0, acc_phase = 0;
+            const uint32_t idesc = make_idesc_sp_f16(p.bf16, kTileRows, kBNSub, 1);
+            int sa = 0, sb = 0;
+            uint32_t pha = 0, phb = 0, acc_phase = 0;
             for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
+                int tm, tn;
+                tile_coords(t, num_m, num_n, tm, tn);
+                const int nsub = (tn * kBN + kBNSub < p.N) ? kNT : 1;
                 if (!mbar_wait(bar_acc_empty, acc_phase ^ 1u)) {
                     report_timeout(p.status, abort_flag, 3);
                     break;
                 }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base;
                 bool ok = true;
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(bar_full + 8 * s, phase)) {
-                        report_timeout(p.status, abort_flag, 2);
-                        ok = false;
-                        break;
-                    }
-                    if (!mbar_wait(bar_a_ready + 8 * s, phase)) {
+                for (int kb = 0; kb < kblocks && ok; ++kb) {
+                    if (!mbar_wait(bar_a_ready + 8 * sa, pha)) {
                         report_timeout(p.status, abort_flag, 6);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t e_cols = tmem_base + (uint32_t)(kECol0 + 4 * s);
-                    tc_cp_128x128b<G>(e_cols, make_smem_desc(smem_e + s * kEBytes, 128, 128, kSwizzleNone));
-                    const uint64_t adesc = make_smem_desc(smem_a + s * kABytes, 16, 1024, kSwizzle128B);
-                    const uint64_t bdesc = make_smem_desc(smem_b + s * kBBytes, kBAtomBytes, 1024, kSwizzle128B);
+                    const uint32_t e_cols = tmem_base + (uint32_t)(kECol0 + 4 * sa);
+                    tc_cp_128x128b<G>(e_cols, make_smem_desc(smem_e + sa * kEBytes, 128, 128, kSwizzleNone));
+                    const uint64_t adesc = make_smem_desc(smem_a + sa * kABytes, 16, 1024, kSwizzle128B);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        tc_mma_sp_f16<G>(tmem_d, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 256), idesc | (uint32_t)(j & 1),
-                                         e_cols + (uint32_t)(j & 2), (kb | j) != 0 ? 1u : 0u);
-                    tc_commit_pair(bar_empty + 8 * s, 3);
-                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                    for (int half = 0; half < 2; ++half) {
+                        if (!mbar_wait(bar_b_full + 8 * sb, phb)) {
+                            report_timeout(p.status, abort_flag, 2);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) {
+                            const int j = 2 * half + jj;   // K = 32 step within the k-block
+                            for (int n = 0; n < nsub; ++n) {
+                                // B: N-major, 128-byte swizzle; 64-column atoms kBAtomBytes apart, 8-k-row groups
+                                // 1024 bytes apart, 32 k-rows (4096 bytes) per step
+                                const uint64_t bdesc =
+                                    make_smem_desc(smem_b + sb * kBBytes + n * kBSubBytes, kBAtomBytes, 1024, kSwizzle128B);
+                                tc_mma_sp_f16<G>(tmem_base + (uint32_t)(n * kBNSub), adesc + (uint64_t)(j * 2),
+                                                 bdesc + (uint64_t)(jj * 256), idesc | (uint32_t)(j & 1),
+                                                 e_cols + (uint32_t)(j & 2), (kb | j) != 0 ? 1u : 0u);
+                            }
+                        }
+                        tc_commit_pair(bar_b_empty + 8 * sb, 3);
+                        if (++sb == kBStages) { sb = 0; phb ^= 1u; }
+                    }
+                    if (!ok) break;
+                    tc_commit_pair(bar_a_free + 8 * sa, 3);
+                    if (++sa == kAStages) { sa = 0; pha ^= 1u; }
                 }
                 if (!ok) break;
                 tc_commit_pair(bar_acc_full, 3);
@@ -209,8 +241,9 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
             uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
             const bool row_ok = row < p.M;
             const bool wide = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * 2)) & 31u) == 0;
+            const int nchunks = (min(kBN, p.N - col0) + 31) / 32;   // accumulator columns past N were never written
 #pragma unroll 1
-            for (int k = 0; k < kBN / 32; ++k) {
+            for (int k = 0; k < nchunks; ++k) {
                 uint32_t r[32];
                 tc_ld_32x32b_x32(tacc + (uint32_t)(32 * k), r);
                 tc_wait_ld();
@@ -309,7 +342,7 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
             // the codes sit in the top byte of each result: 16 columns = one 16-bit word per row
             const uint32_t word = __byte_perm(__byte_perm(ca0, ca1, 0x0073), __byte_perm(cb0, cb1, 0x0073), 0x5410);
 
-            if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u)) {
+            if (!mbar_wait(bar_a_free + 8 * s, phase ^ 1u)) {
                 if (lane == 0) report_timeout(p.status, abort_flag, 5);
                 break;
             }
@@ -320,7 +353,7 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
             fence_proxy_async_shared();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(a_ready_leader + 8 * s);
-            if (++s == STAGES) { s = 0; phase ^= 1u; }
+            if (++s == kAStages) { s = 0; phase ^= 1u; }
 
 #pragma unroll
             for (int i = 0; i < 2; ++i)
@@ -363,7 +396,7 @@ static int launch_prune_in(const CUtensorMap& tm_b, const PruneInParams& pp, cud
         }
     }
     const int num_m = (pp.g.M + 255) / 256;
-    const int num_n = (pp.g.N + pin::kBN - 1) / pin::kBN;
+    const int num_n = (pp.g.N + pin::kBN - 1) / pin::kBN;   // 480-column tiles
     const int tiles = num_m * num_n;
     int units = sm_count() / pin::kG;
     if (units > tiles) units = tiles;
@@ -411,7 +444,7 @@ extern "C" int s24_spmm_prune_in(const void* A, int64_t lda, const void* B, void
 
     CUtensorMap tm_b;
     const CUtensorMapDataType dt = dtype == S24_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    int rc = make_map_2d(&tm_b, dt, 2, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kBlockK, CU_TENSOR_MAP_SWIZZLE_128B, "B");
+    int rc = make_map_2d(&tm_b, dt, 2, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, pin::kBStageK, CU_TENSOR_MAP_SWIZZLE_128B, "B");
     if (rc) return rc;
 
     PruneInParams pp;

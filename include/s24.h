@@ -218,8 +218,9 @@ S24_API int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void
  * i.e. S24_MODE_SIGNED with S24_TIE_HIGHER; S24_TIE_REFERENCE gives the survivors of the torch
  * function prune_2_4 that the reference checks its kernel against).  Shape rules as for s24_spmm plus
  * lda >= K, lda % 8 == 0.  The result is bit-identical to s24_prune_compress followed by
- * s24_spmm on the 256 x 256 tile.  One tile shape (256 x 256 per CTA pair); every k-block of A
- * is pruned once per 256 columns of C, so for large N the two-kernel path is the faster one.
+ * s24_spmm on the 512 x 224 tile (same MMA shape).  One tile shape (256 x 480 per CTA pair, two
+ * column sub-tiles sharing each pruned A stage); every k-block of A is pruned once per 480
+ * columns of C, so for large N the two-kernel path is the faster one.
  */
 S24_API int s24_spmm_prune_in(const void* A, int64_t lda, const void* B, void* C,
                       int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc,

@@ -4,8 +4,8 @@ from the DENSE A in one kernel.
 Checks, as the reference's own (compression/kernels/7.8.1_prune_ws.py:712-716: C against
 prune_2_4(A) @ B): the result is within rtol = atol = 1e-2 of an fp32-accumulated product of the
 oracle-pruned A; with B = I (and the reference's tie rule) it is the oracle-pruned matrix itself;
-and it is bit-identical to the two-kernel path (prune+compress, then the sparse GEMM on the same
-tile shape), which pins the in-kernel values, metadata records and their shared-memory layout.
+and it is bit-identical to the two-kernel path (prune+compress, then the sparse GEMM; a dot product runs over K in the same
+order whatever the MMA's N), which pins the in-kernel values, metadata records and their shared-memory layout.
 """
 import numpy as np
 import pytest
@@ -54,7 +54,7 @@ def test_identity_b_reveals_pruned_a(mods):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 8, 128), (256, 24, 256), (256, 256, 512), (384, 200, 384),
                                    (512, 1032, 1280), (1024, 768, 2048), (256, 256, 16384), (4096, 128, 256),
-                                   (2048, 8192, 2048)])
+                                   (2048, 8192, 2048), (256, 480, 256), (256, 488, 384), (512, 728, 256), (256, 968, 128)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_prune_in_vs_fp32_reference_and_two_kernel_path(mods, M, N, K, dtype):
     s24 = mods["s24"]
@@ -70,7 +70,7 @@ def test_prune_in_vs_fp32_reference_and_two_kernel_path(mods, M, N, K, dtype):
     ref32, _ = _reference(A, B, dtype)
     _check(s24.spmm_prune_in(Ad, Bd, tie="reference"), ref32)
     vals, _, tc = s24.prune_compress(Ad, tie="higher", want_ref=False, want_tc=True)
-    C2 = s24.spmm(vals, tc, Bd, manual_config={"BM": 256, "BN": 256})
+    C2 = s24.spmm(vals, tc, Bd, manual_config={"BM": 512, "BN": 224})
     assert torch.equal(C.view(torch.int16), C2.view(torch.int16))
 
 
@@ -90,7 +90,7 @@ def test_modes_and_tie_rules_on_tie_heavy_input(mods, mode, tie):
     ref32, _ = _reference(A, B, torch.float16, mode, tie)
     _check(C, ref32)
     vals, _, tc = s24.prune_compress(Ad, mode=mode, tie=tie, want_ref=False, want_tc=True)
-    C2 = s24.spmm(vals, tc, Bd, manual_config={"BM": 256, "BN": 256})
+    C2 = s24.spmm(vals, tc, Bd, manual_config={"BM": 512, "BN": 224})
     assert torch.equal(C.view(torch.int16), C2.view(torch.int16))
 
 
