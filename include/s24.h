@@ -3,9 +3,11 @@
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as
  * void*, i.e. a cudaStream_t / CUstream; NULL = the legacy default stream).  Nothing
- * here allocates device memory, synchronises the device or throws: each call enqueues
- * work on the given stream and returns S24_OK or a negative S24_ERR_* code whose text is
- * available (per calling thread) from s24_last_error().
+ * on the compute path allocates device memory, synchronises the device or throws: each
+ * call enqueues work on the given stream and returns S24_OK or a negative S24_ERR_* code
+ * whose text is available (per calling thread) from s24_last_error().  The exceptions are
+ * set-up and debug helpers and say so: s24_peer_alloc / s24_peer_free / s24_peer_open /
+ * s24_peer_close (multi-GPU buffers) and s24_device_status (reads a status word back).
  *
  * The entry points replace, one for one, the GPU work behind these functions of the
  * reference project (paths relative to its root):
