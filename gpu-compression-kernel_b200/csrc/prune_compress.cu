@@ -174,6 +174,46 @@ __global__ void __launch_bounds__(256) meta_convert_kernel(const uint16_t* __res
     }
 }
 
+// Reference layout <-> tensor-core layout, the conversion on the GEMM's path when the caller hands
+// over the reference's E.  Both layouts pair row r (low half) with row r+8 (high half) in one 32-bit
+// word, and the 64 words of a (16-row group, 128-column k-block) are contiguous in both: two
+// adjacent 128-byte lines of E, and a 256-byte run of the k-block's 2 KB record.  Inside that run
+//   E word   s = q*32 + m0*4 + cc          (q = which 64-column half, m0 = r % 8, cc = meta column % 4)
+//   TC word  d = (cc%2)*32 + m0*4 + 2*q + cc/2
+// so a warp moves one block with a coalesced 256-byte load, one exchange between neighbouring
+// lanes and a coalesced 256-byte store (each lane 8 bytes both ways).
+template <bool TO_TC>
+__global__ void __launch_bounds__(256) meta_ref_tc_kernel(const uint2* __restrict__ src, uint2* __restrict__ dst,
+                                                          int64_t row16s, int64_t kblocks)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (blk >= row16s * kblocks) return;
+    const int64_t row16 = blk / kblocks, kb = blk - row16 * kblocks;
+    // in units of uint2 (two words): a block is 32 of them in either layout
+    const int64_t ref_off = (row16 * kblocks + kb) * 32;
+    const int64_t tc_off = (((row16 >> 3) * kblocks + kb) * 8 + (row16 & 7)) * 32;
+    const bool odd = lane & 1;
+    if (TO_TC) {
+        // lane l holds E words (2l, 2l+1): cc = 0,1 (even lane) or 2,3 (odd lane) of (q, m0) = (l/16, (l%16)/2)
+        const uint2 v = src[ref_off + lane];
+        const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, odd ? v.x : v.y, 1);
+        // even lane: {cc=0, cc=2} -> k1 = 0; odd lane: {cc=1, cc=3} -> k1 = 1; TC word pair 2*q + {0,1}
+        const uint2 o = odd ? make_uint2(other, v.y) : make_uint2(v.x, other);
+        const int q = lane >> 4, m0 = (lane & 15) >> 1;
+        dst[tc_off + (odd ? 16 : 0) + m0 * 2 + q] = o;
+    } else {
+        // the inverse: lane l holds TC words (2l, 2l+1) = (k1, m0, q) = (l/16, (l%16)/2, l%2), cc/2 = 0,1
+        const uint2 v = src[tc_off + lane];
+        const int k1 = lane >> 4, m0 = (lane & 15) >> 1, q = lane & 1;
+        // E wants {cc = 2h, 2h+1} together: cc = 2*(cc/2) + k1, so lanes l and l^16 exchange
+        const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, k1 ? v.x : v.y, 16);
+        // k1 = 0 lane keeps cc/2 = 0: {cc=0 (own x), cc=1 (partner's x)}; k1 = 1 lane keeps cc/2 = 1: {cc=2 (partner's y), cc=3 (own y)}
+        const uint2 o = k1 ? make_uint2(other, v.y) : make_uint2(v.x, other);
+        dst[ref_off + q * 16 + m0 * 2 + k1] = o;
+    }
+}
+
 // ---------------------------------------------------------------- gathered shards -> row-major
 
 // An all-gather of column shards arrives shard-major, (G, rows, nl); the caller wants (rows, G*nl).
@@ -320,6 +360,20 @@ extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int
     const int64_t pairs = (M / 2) * ncols;
     const int64_t blocks = (pairs + 255) / 256;
     if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "meta_convert: matrix too large for one launch");
+    const bool ref_tc = (from_layout == S24_META_REF && to_layout == S24_META_TC) ||
+                        (from_layout == S24_META_TC && to_layout == S24_META_REF);
+    if (ref_tc && aligned(src, 8) && aligned(dst, 8)) {
+        // one warp per (16-row group, k-block): 64 words each
+        const int64_t warps = (M / 16) * (K / 128);
+        const unsigned grid = (unsigned)((warps + 7) / 8);
+        if (to_layout == S24_META_TC)
+            meta_ref_tc_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+                static_cast<const uint2*>(src), static_cast<uint2*>(dst), M / 16, K / 128);
+        else
+            meta_ref_tc_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+                static_cast<const uint2*>(src), static_cast<uint2*>(dst), M / 16, K / 128);
+        return check_cuda(cudaGetLastError(), "meta_convert launch");
+    }
     meta_convert_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(src), from_layout, static_cast<uint16_t*>(dst), to_layout, M, ncols);
     return check_cuda(cudaGetLastError(), "meta_convert launch");

@@ -10,8 +10,8 @@
 //
 //   * warp 0: TMA producer for B only, a 4-stage ring of 64 k-rows x 2 x 120 columns per CTA;
 //   * warps 6-21: prune warps.  Each owns 16 rows x 64 columns of this CTA's 128-row slab.  Per
-//     k-block each lane reads 2 x 32 bytes of dense A straight from global memory (the loads of
-//     the next two k-blocks are in flight while the current one is ranked), ranks them with the same
+//     k-block each lane reads 2 x 32 bytes of dense A straight from global memory (the next
+//     k-block's loads are issued before the current one is ranked), ranks them with the same
 //     packed half2 arithmetic as the standalone prune+compress kernel and stores
 //       - the surviving values into the A operand stage (a 4-stage ring of its own) in the
 //         128-byte-swizzled K-major form a TMA load of precompressed values would have produced,
@@ -312,40 +312,27 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
             return pp.A + row * pp.lda + h * 64 + jq * 16;
         };
 
-        // position of this warp in its sequence of (tile, k-block) work items
-        struct Item {
-            int t, kb;
-            const uint16_t* ptr;
-            bool valid, have;
-        };
-        auto next_item = [&](const Item& c) -> Item {
-            Item n = c;
-            if (!c.have) return n;
-            n.kb = c.kb + 1;
-            n.ptr = c.ptr + kBlockK;
-            if (n.kb == kblocks) {
-                n.kb = 0;
-                n.t = c.t + num_units;
-                n.have = n.t < num_tiles;
-                if (n.have) n.ptr = tile_ptr(n.t, n.valid);
-            }
-            return n;
-        };
-
         int s = 0;
         uint32_t phase = 0;
-        uint32_t nxt2[2][8];
-        Item i0 = {unit, 0, nullptr, false, unit < num_tiles};
-        if (i0.have) {
-            i0.ptr = tile_ptr(i0.t, i0.valid);
-            fetch(i0.ptr, i0.valid, cur);
+        int t = unit, kb = 0;
+        bool have = t < num_tiles, valid = false, nvalid = false;
+        const uint16_t* ptr = nullptr;
+        if (have) {
+            ptr = tile_ptr(t, valid);
+            fetch(ptr, valid, cur);
         }
-        Item i1 = next_item(i0);
-        if (i1.have) fetch(i1.ptr, i1.valid, nxt);
-        while (i0.have && !*abort_flag) {
-            // two k-blocks of loads stay in flight while this one is ranked
-            const Item i2 = next_item(i1);
-            if (i2.have) fetch(i2.ptr, i2.valid, nxt2);
+        while (have && !*abort_flag) {
+            // issue the next k-block's loads before working on this one
+            int nt = t, nkb = kb + 1;
+            const uint16_t* nptr = ptr + kBlockK;
+            nvalid = valid;
+            if (nkb == kblocks) {
+                nkb = 0;
+                nt = t + num_units;
+                if (nt < num_tiles) nptr = tile_ptr(nt, nvalid);
+            }
+            const bool have_next = nt < num_tiles;
+            if (have_next) fetch(nptr, nvalid, nxt);
 
             uint32_t va[4], vb[4];
             const uint32_t ca0 = prune_compress_8<DT, MODE>(cur[0][0], cur[0][1], cur[0][2], cur[0][3], pp.tie, va[0], va[1]);
@@ -371,12 +358,12 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    cur[i][j] = nxt[i][j];
-                    nxt[i][j] = nxt2[i][j];
-                }
-            i0 = i1;
-            i1 = i2;
+                for (int j = 0; j < 8; ++j) cur[i][j] = nxt[i][j];
+            t = nt;
+            kb = nkb;
+            ptr = nptr;
+            valid = nvalid;
+            have = have_next;
         }
     }
 

@@ -132,7 +132,7 @@ def test_error_behaviour_matches_reference(mods):
     assert v.shape == d.shape and m.numel() == 0
 
 
-@pytest.mark.parametrize("M,K", [(128, 128), (256, 384), (1024, 2048)])
+@pytest.mark.parametrize("M,K", [(128, 128), (256, 384), (384, 640), (1024, 2048), (2176, 1152)])
 def test_meta_layout_round_trips(mods, M, K):
     s24 = mods["s24"]
     rng = np.random.default_rng(M + K)
