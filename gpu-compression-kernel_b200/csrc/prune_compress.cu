@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
     if (p.meta_tc != nullptr) {
         const int64_t tile = row16 >> 3;
         const int m2 = (int)(row16 & 7);
-        uint32_t* rec = p.meta_tc + ((tile * (p.K >> 7) + cb) * 128 + m0 + 16 * m2) * 4 + jj;
+        uint32_t* rec = p.meta_tc + ((tile * p.col_blocks + cb) * 128 + m0 + 16 * m2) * 4 + jj;
         rec[0] = w0;       // lane L = m0 + 16*m2      (k1 = 0)
         rec[32] = w1;      // lane L = m0 + 8 + 16*m2  (k1 = 1)
     }
@@ -146,7 +146,7 @@ __host__ __device__ __forceinline__ int64_t meta_index(int layout, int64_t r, in
     const int64_t t = r / 128, m2 = (r % 128) / 16, hi = (r / 8) % 2, m0 = r % 8;
     const int64_t kb = c / 8, j = (c % 8) / 2, k1 = c % 2;
     const int64_t lane = m0 + 8 * k1 + 16 * m2;
-    return 2 * (((t * (ncols / 8) + kb) * 128 + lane) * 4 + j) + hi;
+    return 2 * (((t * ((ncols + 7) / 8) + kb) * 128 + lane) * 4 + j) + hi;   // ceil(K / 128) k-blocks per tile
 }
 
 __global__ void __launch_bounds__(256) meta_convert_kernel(const uint16_t* __restrict__ src, int from,
@@ -246,8 +246,6 @@ static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld
     if (M % 32 != 0) return fail(S24_ERR_SHAPE, "Number of rows of dense matrix %lld must be divisible by 32", (long long)M);
     if (K % 64 != 0) return fail(S24_ERR_SHAPE, "Number of columns of dense matrix %lld must be divisible by 64", (long long)K);
     if (ld < K || ld % 8 != 0) return fail(S24_ERR_SHAPE, "prune_compress: row stride %lld must be >= K and a multiple of 8", (long long)ld);
-    if (meta_tc != nullptr && (M % 128 != 0 || K % 128 != 0))
-        return fail(S24_ERR_SHAPE, "prune_compress: tensor-core metadata needs M %% 128 == 0 and K %% 128 == 0 (got %lld x %lld)", (long long)M, (long long)K);
     if (!aligned(A, 16) || !aligned(vals, 16) || !aligned(meta_ref, 16) || !aligned(meta_tc, 16))
         return fail(S24_ERR_INVALID_ARG, "prune_compress: pointers must be 16-byte aligned");
     if (M == 0 || K == 0) return S24_OK;
@@ -341,7 +339,7 @@ extern "C" int s24_prune(const void* A, void* out, int64_t numel, int dtype, int
 extern "C" size_t s24_meta_tc_bytes(int64_t M, int64_t K)
 {
     if (M <= 0 || K <= 0) return 0;
-    return (size_t)(M * K / 8);
+    return (size_t)(((M + 127) / 128) * ((K + 127) / 128)) * 2048;   // one 2 KB record per (128-row tile, 128-column block)
 }
 
 extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int to_layout, int64_t M, int64_t K,
@@ -352,8 +350,6 @@ extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int
         return fail(S24_ERR_INVALID_ARG, "meta_convert: bad layout");
     if (M < 0 || K < 0 || M % 32 != 0 || K % 64 != 0)
         return fail(S24_ERR_SHAPE, "meta_convert: needs M %% 32 == 0 and K %% 64 == 0 (got %lld x %lld)", (long long)M, (long long)K);
-    if ((from_layout == S24_META_TC || to_layout == S24_META_TC) && (M % 128 != 0 || K % 128 != 0))
-        return fail(S24_ERR_SHAPE, "meta_convert: tensor-core layout needs M %% 128 == 0 and K %% 128 == 0 (got %lld x %lld)", (long long)M, (long long)K);
     if (!aligned(src, 4) || !aligned(dst, 4)) return fail(S24_ERR_INVALID_ARG, "meta_convert: pointers must be 4-byte aligned");
     if (M == 0 || K == 0) return S24_OK;
     const int64_t ncols = K / 16;
@@ -362,7 +358,7 @@ extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int
     if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "meta_convert: matrix too large for one launch");
     const bool ref_tc = (from_layout == S24_META_REF && to_layout == S24_META_TC) ||
                         (from_layout == S24_META_TC && to_layout == S24_META_REF);
-    if (ref_tc && aligned(src, 8) && aligned(dst, 8)) {
+    if (ref_tc && K % 128 == 0 && aligned(src, 8) && aligned(dst, 8)) {   // whole k-blocks: two E lines per block
         // one warp per (16-row group, k-block): 64 words each
         const int64_t warps = (M / 16) * (K / 128);
         const unsigned grid = (unsigned)((warps + 7) / 8);

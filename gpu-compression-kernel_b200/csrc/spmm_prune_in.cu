@@ -110,7 +110,7 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
     const int num_tiles = num_m * num_n;
     const int num_units = (int)gridDim.x / G;
     const int unit = (int)blockIdx.x / G;
-    const int kblocks = p.K / kBlockK;
+    const int kblocks = (p.K + kBlockK - 1) / kBlockK;   // a last block of 64 is padded with zeros
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kBStages; ++s) {
@@ -319,7 +319,7 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
         const uint16_t* ptr = nullptr;
         if (have) {
             ptr = tile_ptr(t, valid);
-            fetch(ptr, valid, cur);
+            fetch(ptr, valid && h * 64 < p.K, cur);
         }
         while (have && !*abort_flag) {
             // issue the next k-block's loads before working on this one
@@ -332,7 +332,7 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
                 if (nt < num_tiles) nptr = tile_ptr(nt, nvalid);
             }
             const bool have_next = nt < num_tiles;
-            if (have_next) fetch(nptr, nvalid, nxt);
+            if (have_next) fetch(nptr, nvalid && nkb * kBlockK + h * 64 < p.K, nxt);   // beyond K: zeros
 
             uint32_t va[4], vb[4];
             const uint32_t ca0 = prune_compress_8<DT, MODE>(cur[0][0], cur[0][1], cur[0][2], cur[0][3], pp.tie, va[0], va[1]);
@@ -430,8 +430,8 @@ extern "C" int s24_spmm_prune_in(const void* A, int64_t lda, const void* B, void
     if (mode != S24_MODE_SIGNED && mode != S24_MODE_MAGNITUDE) return fail(S24_ERR_INVALID_ARG, "%s: bad mode %d", who, mode);
     if (tie != S24_TIE_REFERENCE && tie != S24_TIE_LOWER && tie != S24_TIE_HIGHER)
         return fail(S24_ERR_INVALID_ARG, "%s: bad tie rule %d", who, tie);
-    if (M <= 0 || N <= 0 || K <= 0 || M % 128 != 0 || K % 128 != 0 || N % 8 != 0)
-        return fail(S24_ERR_SHAPE, "%s: needs M %% 128 == 0, K %% 128 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)", who,
+    if (M <= 0 || N <= 0 || K <= 0 || M % 32 != 0 || K % 64 != 0 || N % 8 != 0)
+        return fail(S24_ERR_SHAPE, "%s: needs M %% 32 == 0, K %% 64 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)", who,
                     (long long)M, (long long)N, (long long)K);
     if (M > 0x7FFFFF00ll || N > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return fail(S24_ERR_SHAPE, "%s: dimension too large", who);
     if (lda < K || lda % 8 != 0 || ldb < N || ldb % 8 != 0 || ldc < N || ldc % 8 != 0)

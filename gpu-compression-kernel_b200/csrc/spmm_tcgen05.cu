@@ -141,7 +141,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const int num_tiles = num_m * num_n;
     const int num_units = (int)gridDim.x / G;
     const int unit = (int)blockIdx.x / G;
-    const int kblocks = p.K / kBlockK;
+    const int kblocks = (p.K + kBlockK - 1) / kBlockK;   // a last block of 64 reads zeros beyond K
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -454,7 +454,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         const int64_t t128 = row >> 7;
                         const int m2 = (int)((row >> 4) & 7);
                         const int kb = cidx >> 3, j = (cidx & 7) >> 1;
-                        uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)(p.N >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
+                        uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)((p.N + 127) >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
                         rec[0] = w0;
                         rec[32] = w1;
                     }
@@ -547,7 +547,7 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
         rc = make_map_2d(&tm_b, dt, 2, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, kBlockK,
                          CU_TENSOR_MAP_SWIZZLE_128B, "B");
     if (rc) return rc;
-    const uint64_t records = (uint64_t)(g.M / 128) * (uint64_t)(g.K / 128);
+    const uint64_t records = (uint64_t)((g.M + 127) / 128) * (uint64_t)((g.K + 127) / 128);
     rc = make_map_2d(&tm_e, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, g.meta_tc, 128, records * 4, 512, 128, 4,
                      CU_TENSOR_MAP_SWIZZLE_NONE, "metadata");
     if (rc) return rc;
@@ -619,8 +619,10 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     if (vals == nullptr || meta_tc == nullptr || B == nullptr || (!prune_out && C == nullptr) || (prune_out && c_vals == nullptr))
         return fail(S24_ERR_INVALID_ARG, "%s: null pointer", who);
     if (dtype != S24_FP16 && dtype != S24_BF16) return fail(S24_ERR_INVALID_ARG, "%s: bad dtype %d", who, dtype);
-    if (M <= 0 || N <= 0 || K <= 0 || M % 128 != 0 || K % 128 != 0 || N % 8 != 0)
-        return fail(S24_ERR_SHAPE, "%s: needs M %% 128 == 0, K %% 128 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)", who,
+    // the shapes compress_dense_to_sparse accepts (compress_2_4.py:49-65): tiles of 128 rows and
+    // k-blocks of 128 that are only partly covered read zeros (TMA out-of-range fill) for the rest
+    if (M <= 0 || N <= 0 || K <= 0 || M % 32 != 0 || K % 64 != 0 || N % 8 != 0)
+        return fail(S24_ERR_SHAPE, "%s: needs M %% 32 == 0, K %% 64 == 0, N %% 8 == 0 (got M=%lld N=%lld K=%lld)", who,
                     (long long)M, (long long)N, (long long)K);
     if (prune_out && N % 128 != 0)
         return fail(S24_ERR_SHAPE, "%s: needs N %% 128 == 0 (got N=%lld)", who, (long long)N);
@@ -701,6 +703,15 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 512x224, 256x256, 256x128, 128x128)", who, bm, bn);
 }
 
+// Where the matrix covers the last 128-row tile or 128-column block only partly, the conversion
+// leaves the words outside the matrix untouched; give them a valid code before it runs (the
+// values they index are zero).  An asynchronous memset: no allocation, legal under stream capture.
+static int prefill_partial_records(void* meta_tc, int64_t M, int64_t K, cudaStream_t stream)
+{
+    if (M <= 0 || K <= 0 || (M % 128 == 0 && K % 128 == 0)) return S24_OK;
+    return check_cuda(cudaMemsetAsync(meta_tc, 0x44, s24_meta_tc_bytes(M, K), stream), "metadata workspace prefill");
+}
+
 }  // namespace s24
 
 using namespace s24;
@@ -734,7 +745,9 @@ extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const v
         return fail(S24_ERR_INVALID_ARG, "spmm_ref_meta: workspace of %zu bytes needed, %zu given", s24_meta_tc_bytes(M, K),
                     workspace_bytes);
     if (!aligned(workspace, 16)) return fail(S24_ERR_INVALID_ARG, "spmm_ref_meta: workspace must be 16-byte aligned");
-    int rc = s24_meta_convert(meta_ref, S24_META_REF, workspace, S24_META_TC, M, K, stream);
+    int rc = prefill_partial_records(workspace, M, K, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+    rc = s24_meta_convert(meta_ref, S24_META_REF, workspace, S24_META_TC, M, K, stream);
     if (rc) return rc;
     return run_spmm(vals, workspace, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
 }
@@ -780,7 +793,9 @@ extern "C" int s24_spmm_ref_meta_noalloc(const void* vals, const void* meta_ref,
                     (long long)M, (long long)K, need, (size_t)S24_STATIC_SCRATCH_BYTES);
     void* scratch = static_scratch_address();   // first call per device: address lookup, no allocation
     if (scratch == nullptr) return S24_ERR_CUDA;
-    int rc = s24_meta_convert(meta_ref, S24_META_REF, scratch, S24_META_TC, M, K, stream);
+    int rc = prefill_partial_records(scratch, M, K, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+    rc = s24_meta_convert(meta_ref, S24_META_REF, scratch, S24_META_TC, M, K, stream);
     if (rc) return rc;
     return run_spmm(vals, scratch, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
 }

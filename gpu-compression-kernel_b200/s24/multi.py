@@ -35,17 +35,17 @@ def shard_bounds(n: int, world: int, rank: int, multiple: int = 8) -> Tuple[int,
 
 
 def row_panels(m: int, panels: int, multiple: int = 128) -> List[Tuple[int, int]]:
-    """split M rows into at most `panels` contiguous panels whose sizes are multiples of
-    `multiple` (the kernel's M granularity)"""
-    if m % multiple != 0:
-        raise ValueError(f"M={m} must be a multiple of {multiple}")
-    units = m // multiple
+    """split M rows into at most `panels` contiguous panels that start on multiples of `multiple`
+    (the row granularity of the tensor-core metadata records); only the last panel may end off one"""
+    if m <= 0 or m % 32 != 0:
+        raise ValueError(f"M={m} must be a positive multiple of 32")
+    units = -(-m // multiple)
     panels = max(1, min(panels, units))
     base, extra = divmod(units, panels)
     out, r = [], 0
     for i in range(panels):
         size = (base + (1 if i < extra else 0)) * multiple
-        out.append((r, r + size))
+        out.append((r, min(r + size, m)))
         r += size
     return out
 
@@ -267,5 +267,5 @@ class NShardedSpmm:
     def _meta_rows(self, r0: int, r1: int) -> torch.Tensor:
         """tensor-core metadata of rows [r0, r1): records are ordered [row tile of 128][k block],
         512 int32 each, so a row panel is a contiguous slice"""
-        per_tile = (self.K // 128) * 512
-        return self.meta_tc[(r0 // 128) * per_tile:(r1 // 128) * per_tile]
+        per_tile = -(-self.K // 128) * 512
+        return self.meta_tc[(r0 // 128) * per_tile:-(-r1 // 128) * per_tile]

@@ -82,6 +82,19 @@ def meta_tc_numel(M: int, K: int) -> int:
     return int(L.lib().s24_meta_tc_bytes(M, K)) // 4
 
 
+_TC_FILLER = 0x44444444   # a valid 2:4 code in every nibble
+
+
+def _new_meta_tc(M: int, K: int, device) -> torch.Tensor:
+    """Tensor-core-layout buffer.  Records are whole (128-row tile, 128-column block) units; when the
+    matrix covers the last ones only partly, the words outside it are never written by the kernels,
+    so they are pre-set to a valid code (the values they index are zero)."""
+    n = meta_tc_numel(M, K)
+    if M % 128 == 0 and K % 128 == 0:
+        return torch.empty((n,), dtype=torch.int32, device=device)
+    return torch.full((n,), _TC_FILLER, dtype=torch.int32, device=device)
+
+
 def prune(t: torch.Tensor, mode: str = "signed", tie: str = "reference") -> torch.Tensor:
     """2:4 prune along the last dimension; new tensor (compression/prune.py:57-96)."""
     if t.size(-1) % 4 != 0:
@@ -125,7 +138,7 @@ def compress(dense: torch.Tensor, want_ref: bool = True, want_tc: bool = False):
     d = _row_major(dense)
     vals = torch.empty((m, k // 2), dtype=dense.dtype, device=dense.device)
     e = torch.empty((m // 16, k), dtype=torch.int16, device=dense.device) if want_ref else None
-    tc = torch.empty((meta_tc_numel(m, k),), dtype=torch.int32, device=dense.device) if want_tc else None
+    tc = _new_meta_tc(m, k, dense.device) if want_tc else None
     if m * k:
         with _on_device(dense):
             L.check(L.lib().s24_compress(_p(d), m, k, d.stride(0), _DT[dense.dtype], _p(vals), _p(e), _p(tc),
@@ -144,7 +157,7 @@ def prune_compress(A: torch.Tensor, mode: str = "signed", tie: str = "reference"
     a = _row_major(A)
     vals = torch.empty((m, k // 2), dtype=A.dtype, device=A.device)
     e = torch.empty((m // 16, k), dtype=torch.int16, device=A.device) if want_ref else None
-    tc = torch.empty((meta_tc_numel(m, k),), dtype=torch.int32, device=A.device) if want_tc else None
+    tc = _new_meta_tc(m, k, A.device) if want_tc else None
     if m * k:
         with _on_device(A):
             L.check(L.lib().s24_prune_compress(_p(a), m, k, a.stride(0), _DT[A.dtype], _MODE[mode], _TIE[tie],
@@ -160,7 +173,7 @@ def meta_convert(src: torch.Tensor, from_layout: str, to_layout: str, M: int, K:
     _require_cuda(src)
     src = src.contiguous()
     if to_layout == "tc":
-        dst = torch.empty((meta_tc_numel(M, K),), dtype=torch.int32, device=src.device)
+        dst = _new_meta_tc(M, K, src.device)
     elif to_layout == "ref":
         dst = torch.empty((M // 16, K), dtype=torch.int16, device=src.device)
     else:
@@ -189,9 +202,17 @@ def _check_gemm(vals: torch.Tensor, B: torch.Tensor) -> Tuple[int, int, int]:
     if vals.dtype != B.dtype:
         raise RuntimeError(f"operand dtypes differ: {vals.dtype} vs {B.dtype}")
     _dtype_code(vals)
-    if M % 128 != 0 or K % 128 != 0 or N % 8 != 0:
-        raise RuntimeError(f"sparse matmul needs M % 128 == 0, K % 128 == 0, N % 8 == 0 (got M={M}, N={N}, K={K})")
+    if M % 32 != 0 or K % 64 != 0 or N % 8 != 0:
+        raise RuntimeError(f"sparse matmul needs M % 32 == 0, K % 64 == 0, N % 8 == 0 (got M={M}, N={N}, K={K})")
     return M, N, K
+
+
+def _check_meta_tc(meta: torch.Tensor, M: int, K: int) -> None:
+    """the kernel reads whole records: a short buffer would be read past its end"""
+    need = meta_tc_numel(M, K) * 4
+    have = meta.numel() * meta.element_size()
+    if have < need or not meta.is_contiguous():
+        raise RuntimeError(f"tensor-core metadata of a ({M}, {K}) matrix needs {need} contiguous bytes, got {have}")
 
 
 _TILE_CANDIDATES = ({"BM": 512, "BN": 224}, {"BM": 256, "BN": 256}, {"BM": 256, "BN": 128}, {"BM": 128, "BN": 128})
@@ -261,6 +282,7 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
         if c.stride(1) != 1 or c.stride(0) % 8 != 0 or tuple(c.shape) != (M, N) or c.dtype != vals.dtype:
             raise RuntimeError(f"`out` must be a row-major ({M}, {N}) {vals.dtype} tensor")
         with _on_device(vals):
+            _check_meta_tc(meta, M, K)
             L.check(L.lib().s24_spmm_bt(_p(v), _p(meta), _p(B), _p(c), M, N, K, B.stride(1), c.stride(0),
                                         _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
         return c
@@ -282,13 +304,14 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
             manual_config = _autotune(v, meta, b, c, M, N, K)
         cfg = _tile_cfg(manual_config)
         if meta_layout == "tc":
+            _check_meta_tc(meta, M, K)
             L.check(L.lib().s24_spmm(_p(v), _p(meta), _p(b), _p(c), M, N, K, b.stride(0), c.stride(0),
                                      _DT[vals.dtype], cfg, _stream(vals)))
         elif meta_layout == "ref":
             if meta.numel() != M * K // 16:
                 raise RuntimeError(f"E has {meta.numel()} elements, expected {M * K // 16} for ({M}, {K})")
             if workspace is None:
-                workspace = torch.empty((meta_tc_numel(M, K),), dtype=torch.int32, device=vals.device)
+                workspace = _new_meta_tc(M, K, vals.device)
             L.check(L.lib().s24_spmm_ref_meta(_p(v), _p(meta.contiguous()), _p(b), _p(c), M, N, K, b.stride(0),
                                               c.stride(0), _DT[vals.dtype], cfg, _p(workspace),
                                               workspace.numel() * 4, _stream(vals)))
@@ -312,13 +335,14 @@ def spmm_prune_out(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta
         meta_tc = meta_convert(meta, "ref", "tc", M, K)
     elif meta_layout == "tc":
         meta_tc = meta
+        _check_meta_tc(meta_tc, M, K)
     else:
         raise ValueError(f"unknown metadata layout {meta_layout!r}")
     v = vals.contiguous()
     b = _row_major(B)
     cv = torch.empty((M, N // 2), dtype=vals.dtype, device=vals.device)
     ce = torch.empty((M // 16, N), dtype=torch.int16, device=vals.device) if want_ref else None
-    ct = torch.empty((meta_tc_numel(M, N),), dtype=torch.int32, device=vals.device) if want_tc else None
+    ct = _new_meta_tc(M, N, vals.device) if want_tc else None
     with _on_device(vals):
         L.check(L.lib().s24_spmm_prune_out(_p(v), _p(meta_tc), _p(b), _p(cv), _p(ce), _p(ct), M, N, K,
                                            b.stride(0), _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
@@ -340,8 +364,8 @@ def spmm_prune_in(A: torch.Tensor, B: torch.Tensor, mode: str = "signed", tie: s
         raise RuntimeError(f"A and B must both be float16 or bfloat16 (got {A.dtype}, {B.dtype})")
     M, K = A.shape
     N = B.shape[1]
-    if M <= 0 or M % 128 != 0 or K <= 0 or K % 128 != 0 or N <= 0 or N % 8 != 0:
-        raise RuntimeError(f"needs M % 128 == 0, K % 128 == 0, N % 8 == 0 (got M={M}, N={N}, K={K})")
+    if M <= 0 or M % 32 != 0 or K <= 0 or K % 64 != 0 or N <= 0 or N % 8 != 0:
+        raise RuntimeError(f"needs M % 32 == 0, K % 64 == 0, N % 8 == 0 (got M={M}, N={N}, K={K})")
     a = _row_major(A)
     b = _row_major(B)
     c = out if out is not None else torch.empty((M, N), dtype=A.dtype, device=A.device)
@@ -368,6 +392,7 @@ def spmm_scatter(vals: torch.Tensor, meta_tc: torch.Tensor, B: torch.Tensor, dst
     b = _row_major(B)
     arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
     with _on_device(vals):
+        _check_meta_tc(meta_tc, M, K)
         L.check(L.lib().s24_spmm_scatter(_p(v), _p(meta_tc), _p(b), arr, len(dst_ptrs), M, N, K, b.stride(0), int(ldc),
                                          _DT[vals.dtype], _stream(vals)))
 

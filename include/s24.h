@@ -36,6 +36,11 @@
  *                     meta[128t+16*m2+m0][8kb+2j+k1] | meta[128t+16*m2+8+m0][8kb+2j+k1] << 16.
  *                     This is the image tcgen05.cp (128x128b) moves into tensor memory for
  *                     four consecutive tcgen05.mma.sp instructions of K = 32.
+ *                     There are ceil(M/128) x ceil(K/128) whole records; where M or K is not a
+ *                     multiple of 128 the words of rows >= M and of columns >= K are not
+ *                     written by the library and must hold valid codes when a GEMM reads them
+ *                     (the values they index read as zero): fill the buffer with 0x44 bytes
+ *                     before the first use, as the Python front end does.
  */
 #ifndef S24_H_
 #define S24_H_
@@ -111,7 +116,7 @@ S24_API int s24_prune(const void* A, void* out, int64_t numel, int dtype, int mo
  * reordered layout to meta_ref ((M/16, K) int16) and/or in the tensor-core layout to
  * meta_tc (s24_meta_tc_bytes(M, K) bytes); either metadata pointer may be NULL.
  * Needs M % 32 == 0, K % 64 == 0 (compress_2_4.py:10,57-65), ld % 8 == 0, 16-byte aligned
- * pointers; meta_tc additionally needs M % 128 == 0 and K % 128 == 0.
+ * pointers.
  */
 S24_API int s24_compress(const void* dense, int64_t M, int64_t K, int64_t ld, int dtype,
                  void* vals, void* meta_ref, void* meta_tc, void* stream);
@@ -125,13 +130,13 @@ S24_API int s24_compress(const void* dense, int64_t M, int64_t K, int64_t ld, in
 S24_API int s24_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld, int dtype, int mode, int tie,
                        void* vals, void* meta_ref, void* meta_tc, void* stream);
 
-/* bytes of a S24_META_TC buffer for an (M, K) matrix: M * K / 8 (one bit per element) */
+/* bytes of a S24_META_TC buffer for an (M, K) matrix: ceil(M/128) * ceil(K/128) * 2048
+ * (= M * K / 8, one bit per element, when both are multiples of 128) */
 S24_API size_t s24_meta_tc_bytes(int64_t M, int64_t K);
 
 /*
  * Convert metadata between layouts (compression/compress_2_4.py:6-30 gives
- * LOGICAL -> REF).  M % 32 == 0 and K % 64 == 0; any side in S24_META_TC needs
- * M % 128 == 0 and K % 128 == 0.  src and dst must not overlap.
+ * LOGICAL -> REF).  M % 32 == 0 and K % 64 == 0.  src and dst must not overlap.
  */
 S24_API int s24_meta_convert(const void* src, int from_layout, void* dst, int to_layout,
                      int64_t M, int64_t K, void* stream);
@@ -140,8 +145,10 @@ S24_API int s24_meta_convert(const void* src, int from_layout, void* dst, int to
  * run_sparse_ws_matmul (compression/gluon_ws_sparse.py:560-613):
  *   C (M, N) = A24 (M, K) . B (K, N), fp32 accumulation, C in the element type of A/B.
  * A24 is given as vals (M, K/2 contiguous) + meta_tc (S24_META_TC).  B has row stride
- * ldb, C row stride ldc (elements).  M % 128 == 0, K % 128 == 0, N % 8 == 0,
- * ldb % 8 == 0, ldc % 8 == 0, 16-byte aligned pointers.
+ * ldb, C row stride ldc (elements).  M % 32 == 0, K % 64 == 0 (every shape
+ * compress_dense_to_sparse accepts; tiles and k-blocks that are only partly covered read
+ * zeros), N % 8 == 0, ldb % 8 == 0, ldc % 8 == 0, 16-byte aligned pointers; meta_tc must
+ * span s24_meta_tc_bytes(M, K).
  */
 S24_API int s24_spmm(const void* vals, const void* meta_tc, const void* B, void* C,
              int64_t M, int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,

@@ -165,13 +165,14 @@ def meta_offsets(M: int, ncols: int) -> np.ndarray:
 
 
 def meta_tc(meta_logical: np.ndarray, K: int) -> np.ndarray:
-    """Logical metadata -> tcgen05 record layout, uint32 (M/128 * K/128 * 512,)."""
+    """Logical metadata -> tcgen05 record layout, uint32 (ceil(M/128) * ceil(K/128) * 512,);
+    words of a partly covered last tile / block that lie outside the matrix are 0x44444444."""
     ml = np.ascontiguousarray(meta_logical, dtype=np.int16)
     M = ml.shape[0]
-    out = np.empty((M // 128 * (K // 128) * 512,), dtype=np.uint32)
+    out = np.empty((-(-M // 128) * -(-K // 128) * 512,), dtype=np.uint32)
     rc = lib().s24o_meta_tc(_p(ml), M, K, _p(out))
     if rc != 0:
-        raise RuntimeError("meta_tc needs M % 128 == 0 and K % 128 == 0")
+        raise RuntimeError("meta_tc needs M % 16 == 0 and K % 64 == 0")
     return out
 
 

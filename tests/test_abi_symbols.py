@@ -44,6 +44,7 @@ def test_ctypes_signatures_cover_the_header(built):
     L = _lib.lib()
     assert L.s24_version() == 1
     assert L.s24_meta_tc_bytes(256, 512) == 256 * 512 // 8
+    assert L.s24_meta_tc_bytes(160, 192) == 2 * 2 * 2048       # whole (128-row, 128-column) records
 
 
 def test_argument_errors_need_no_gpu(built):
@@ -60,7 +61,8 @@ def test_argument_errors_need_no_gpu(built):
     assert L.s24_prune_compress(p, 32, 80, 80, 0, 0, 0, p, p, None, None) == _lib.ERR_SHAPE
     assert L.s24_prune_compress(p, 32, 64, 64, 7, 0, 0, p, p, None, None) == _lib.ERR_INVALID_ARG
     assert L.s24_spmm(p, p, p, p, 100, 128, 128, 128, 128, 0, None, None) == _lib.ERR_SHAPE
-    assert L.s24_meta_convert(p, 1, p, 2, 64, 128, None) == _lib.ERR_SHAPE
+    assert L.s24_meta_convert(p, 1, p, 2, 48, 128, None) == _lib.ERR_SHAPE          # M % 32
+    assert L.s24_spmm(p, p, p, p, 128, 128, 96, 128, 128, 0, None, None) == _lib.ERR_SHAPE   # K % 64
 
 
 def test_cpu_tensors_are_rejected_loudly(built):

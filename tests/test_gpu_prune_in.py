@@ -54,7 +54,8 @@ def test_identity_b_reveals_pruned_a(mods):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 8, 128), (256, 24, 256), (256, 256, 512), (384, 200, 384),
                                    (512, 1032, 1280), (1024, 768, 2048), (256, 256, 16384), (4096, 128, 256),
-                                   (2048, 8192, 2048), (256, 480, 256), (256, 488, 384), (512, 728, 256), (256, 968, 128)])
+                                   (2048, 8192, 2048), (256, 480, 256), (256, 488, 384), (512, 728, 256), (256, 968, 128),
+                                   (32, 8, 64), (160, 72, 192), (416, 496, 320)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_prune_in_vs_fp32_reference_and_two_kernel_path(mods, M, N, K, dtype):
     s24 = mods["s24"]
@@ -123,7 +124,7 @@ def test_rejects_bad_arguments(mods):
     A = torch.zeros((128, 128), dtype=torch.float16, device=DEV)
     B = torch.zeros((128, 64), dtype=torch.float16, device=DEV)
     with pytest.raises(RuntimeError):
-        s24.spmm_prune_in(A[:64], B)                      # M % 128
+        s24.spmm_prune_in(A[:48], B)                      # M % 32
     with pytest.raises(RuntimeError):
         s24.spmm_prune_in(A, B[:, :12])                   # N % 8
     with pytest.raises(RuntimeError):

@@ -60,7 +60,8 @@ def _check_against_oracle(c_vals, c_meta_ref, C32, dtype):
     return float(differ.mean()), float(near_tie.mean())
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 512, 384), (384, 256, 1024), (1024, 1152, 512), (1536, 896, 256)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 512, 384), (384, 256, 1024), (1024, 1152, 512), (1536, 896, 256),
+                                   (160, 256, 192), (32, 128, 64)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
 def test_fused_output_prune(mods, M, N, K, dtype, cfg):

@@ -59,7 +59,9 @@ def test_identity_b_reveals_decompressed_a(mods, cfg):
     assert torch.equal(C.float().cpu(), from_bits(ap, torch.float16).float())   # -0.0 == +0.0
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 8, 128), (256, 24, 256), (256, 256, 512), (384, 200, 384), (512, 1032, 1280), (1024, 768, 2048), (256, 256, 16384), (4096, 128, 256)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 8, 128), (256, 24, 256), (256, 256, 512), (384, 200, 384), (512, 1032, 1280), (1024, 768, 2048), (256, 256, 16384), (4096, 128, 256),
+                                   # every shape compress_dense_to_sparse accepts (M % 32, K % 64): partly covered tiles and k-blocks
+                                   (32, 8, 64), (160, 72, 192), (96, 200, 64), (416, 256, 320), (544, 232, 1088)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("cfg", [None, {"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
 def test_spmm_vs_fp32_reference(mods, M, N, K, dtype, cfg):
@@ -256,3 +258,23 @@ def test_scatter_epilogue_writes_every_destination(mods, M, N, K, dtype):
     assert bool((wide[:, 2 * N + 16:] == 3.0).all()) and bool((wide[M] == 3.0).all())
     assert bool((other[:, N:] == 5.0).all())
     _check(want, _reference(ap, B, dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(32, 16, 64), (160, 72, 192), (416, 256, 320)])
+def test_partly_covered_tiles_through_the_reference_layout_entry(mods, M, N, K):
+    """shapes that are multiples of 32 / 64 but not of 128, through run_sparse_ws_matmul(A_vals, E, B):
+    the library converts E into a caller-sized workspace whose padding words it must make valid itself
+    (the workspace is handed over full of an invalid code on purpose)"""
+    s24 = mods["s24"]
+    dtype = torch.float16
+    A, B, ap, vals, ml, e = _prepare(M, K, N, dtype, 950 + M + N + K)
+    v, E, Bd = from_bits(vals, dtype, DEV), torch.from_numpy(e).to(DEV), B.to(DEV)
+    C = mods["ws"].run_sparse_ws_matmul(v, E, Bd)
+    _status_ok(s24)
+    ref32 = _reference(ap, B, dtype)
+    _check(C, ref32)
+    ws = torch.zeros((s24.meta_tc_numel(M, K),), dtype=torch.int32, device=DEV)   # code 0 is not a valid 2:4 code
+    C2 = s24.spmm(v, E, Bd, meta_layout="ref", workspace=ws)
+    _status_ok(s24)
+    assert torch.equal(C, C2)
+    assert np.array_equal(ws.cpu().numpy().view(np.uint32), oracle.meta_tc(ml, K))

@@ -39,6 +39,8 @@ def test_row_panels():
     assert row_panels(384, 4) == [(0, 128), (128, 256), (256, 384)]
     assert row_panels(28672, 8)[-1][1] == 28672
     assert all((b - a) % 128 == 0 for a, b in row_panels(28672, 8))
+    assert row_panels(160, 4) == [(0, 128), (128, 160)]            # ragged tail stays in the last panel
+    assert row_panels(96, 4) == [(0, 96)]
     with pytest.raises(ValueError):
         row_panels(100, 2)
 
