@@ -278,3 +278,13 @@ def test_partly_covered_tiles_through_the_reference_layout_entry(mods, M, N, K):
     _status_ok(s24)
     assert torch.equal(C, C2)
     assert np.array_equal(ws.cpu().numpy().view(np.uint32), oracle.meta_tc(ml, K))
+
+
+def test_dense_baseline_module_is_importable_and_is_cublas(mods):
+    """the reference's benchmark drivers import gluon_ws_dense beside gluon_ws_sparse; the stand-in
+    is a cuBLAS product"""
+    dense = load_dropin("gluon_ws_dense.py")
+    A = randn((256, 512), torch.float16, 41).to(DEV)
+    B = randn((512, 128), torch.float16, 42).to(DEV)
+    C = dense.run_ws_matmul(A, B, tune=False, manual_config={"BM": 128})
+    assert C.dtype == torch.float16 and torch.equal(C, A @ B)
