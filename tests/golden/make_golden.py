@@ -1,9 +1,8 @@
 """Generate the golden vectors under tests/golden from the reference's own Python code.
 
-Run in a container that mounts the reference project (default /root/reference, or pass
-its root as argv[1]):
+Run where the reference project is checked out, passing its root:
 
-    python tests/golden/make_golden.py [reference_root]
+    python tests/golden/make_golden.py <reference_root>
 
 It imports the reference's ``compression/prune.py`` and ``compression/compress_2_4.py``
 unmodified, runs them on CPU on seeded inputs and stores inputs + outputs as raw 16-bit
@@ -27,7 +26,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py <reference_root>")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "compression"))
 
 from prune import prune_2_4  # noqa: E402  (reference)
