@@ -5,8 +5,7 @@
 // compress_dense_to_sparse (compression/compress_2_4.py:32-161) and its standalone fused
 // kernel ws_tma_compress_2_4_kernel (compression/kernels/11.1_2_kernel_baseline.py:171-203).
 //
-// Fused kernel layout.  A warp works on one 16-row x 128-column block of A at a time (and
-// walks the blocks with a grid stride, about four per warp).  Lane
+// Fused kernel layout.  One warp owns a 16-row x 128-column block of A.  Lane
 // (m0 = lane/4, jj = lane%4) reads rows m0 and m0+8 of the block, 32 consecutive
 // elements each (64 bytes per row, two 256-bit loads), so a warp-wide load covers whole
 // 128-byte lines.  All ranking happens in registers of the owning lane -- no shared memory,
@@ -52,13 +51,13 @@ template <int DT, int MODE, bool LD256>
 __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
 {
     const int lane = threadIdx.x & 31;
-    const int64_t total_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t wt = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wt < p.warp_tiles; wt += total_warps) {
+    const int64_t wt = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wt >= p.warp_tiles) return;
     const int64_t row16 = wt / p.col_blocks;
     const int64_t cb = wt - row16 * p.col_blocks;
     const int m0 = lane >> 2, jj = lane & 3;
     const int64_t col0 = cb * 128 + jj * 32;
-    if (col0 >= p.K) continue;  // K % 128 == 64: the upper two lanes of each row are idle
+    if (col0 >= p.K) return;  // K % 128 == 64: the upper two lanes of each row are idle
     const int64_t rA = row16 * 16 + m0, rB = rA + 8;
 
     uint32_t a_lo[8], a_hi[8], b_lo[8], b_hi[8];
@@ -104,7 +103,6 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
         rec[32] = w1;      // lane L = m0 + 8 + 16*m2  (k1 = 1)
     }
 }
-}
 
 // ---------------------------------------------------------------- dense prune (prune_2_4)
 
@@ -112,9 +110,9 @@ template <int DT, int MODE, bool V128>
 __global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* __restrict__ A, uint16_t* __restrict__ out,
                                                           int64_t numel, int tie)
 {
-    const int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t total = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i8 * 8 < numel; i8 += total) {
     const int64_t base = i8 * 8;
-    if (base >= numel) return;
     uint32_t in[4] = {0, 0, 0, 0}, o[4];
     const bool full = base + 8 <= numel;  // otherwise exactly one group of 4 is left
     if (V128 && full) {
@@ -134,6 +132,7 @@ __global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* __rest
     } else {
         *reinterpret_cast<uint2*>(out + base) = make_uint2(o[0], o[1]);
         if (full) *reinterpret_cast<uint2*>(out + base + 4) = make_uint2(o[2], o[3]);
+    }
     }
 }
 
@@ -266,14 +265,7 @@ static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld
     const int64_t blocks = (p.warp_tiles + 7) / 8;
     if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "prune_compress: matrix too large for one launch");
     const bool ld256ok = aligned(A, 32) && aligned(vals, 32) && (ld % 16 == 0);
-    // Warps walk the tiles with a grid stride.  About four tiles per warp measured best on B200
-    // (16384^2: +7 %, 32768^2: +9 % over one tile per warp: fewer CTA launches, the same dynamic
-    // balance); never fewer CTAs than the device holds at once (8 per SM).
-    int64_t nblocks = (blocks + 3) / 4;
-    const int64_t resident = (int64_t)sm_count() * 8;
-    if (nblocks < resident) nblocks = resident;
-    if (nblocks > blocks) nblocks = blocks;
-    dim3 grid((unsigned)nblocks), block(256);
+    dim3 grid((unsigned)blocks), block(256);
 #define S24_LAUNCH_PC(DT, MODE)                                                              \
     do {                                                                                     \
         if (ld256ok) prune_compress_kernel<DT, MODE, true><<<grid, block, 0, stream>>>(p);   \
@@ -328,7 +320,12 @@ extern "C" int s24_prune(const void* A, void* out, int64_t numel, int dtype, int
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint16_t* a = static_cast<const uint16_t*>(A);
     uint16_t* o = static_cast<uint16_t*>(out);
-    dim3 grid((unsigned)blocks), block(256);
+    // grid stride, about four vectors per thread, never fewer CTAs than the device holds at once
+    int64_t nblocks = (blocks + 3) / 4;
+    const int64_t resident = (int64_t)sm_count() * 8;
+    if (nblocks < resident) nblocks = resident;
+    if (nblocks > blocks) nblocks = blocks;
+    dim3 grid((unsigned)nblocks), block(256);
 #define S24_LAUNCH_PRUNE(DT, MODE)                                                          \
     do {                                                                                    \
         if (v128) prune_dense_kernel<DT, MODE, true><<<grid, block, 0, s>>>(a, o, numel, tie);  \
