@@ -12,11 +12,25 @@ Printed by rank 0, one JSON line:
   value      whole-job dense-equivalent TFLOP/s (2 M N K per GEMM, the reference's
              convention, compression/dev/8.11_benchmark_2_kernel.py:49-50), inputs resident in HBM
   e2e        same metric through the reference-facing call run_sparse_ws_matmul(A, E, B)
-             with pinned HOST buffers: H2D of A values, E and B and D2H of C inside the timed region
-  roofline   the GEMM kernel against 2 x the measured dense bf16 tensor peak
+             with pinned HOST buffers: H2D of A values, E and B and D2H of C inside the timed
+             region; per rank the copy rates, the CPU affinity and a copies-only pass (the host
+             link's ceiling at this number of GPUs)
+  roofline   the GEMM kernel against 2 x the measured dense bf16 tensor peak (burst: the timed
+             region is a few milliseconds long)
+  sustained  the same GEMM back to back for two seconds with the clock sampler inside: ms per
+             step, SM MHz, cycles per step and the fraction of 2 x the measured SUSTAINED peak
+  two_kernel / fused_out   the reference's other headline lines at 8192^3: prune+compress then GEMM
+             (compression/kernels/11.1_2_kernel_baseline.py) and the pruning epilogue with its ratio
+             to the plain GEMM on the same tile (compression/kernels/10.1_prune_acc.py)
   prune_compress   the standalone fused prune+compress kernel at 16384 x 16384 fp16 in GB/s
              (3.125 bytes per element, compression/dev/8.11.1_benchmark_pruning.py:43-52)
-             with its HBM roofline
+             with its HBM roofline; prune_compress_sizes adds 4096^2 (eager, graph replay and
+             cold L2), 32768^2 and bf16
+  cfg1       the reference's CPU-runnable case (2048 x 2048 x 8192), L2-resident: warm and cold-L2 times
+  cfg5       (N > 1 only) the MLP-shaped product W 28672 x 8192 bf16 . X 8192 x 65536 with the output
+             columns split over the ranks (strong scaling): sharded, replicated by NCCL all-gather
+             and replicated by the GEMM's own peer-store epilogue, each checked against locally
+             recomputed shards
   cpu_baseline     the CPU port of the reference path timed on this box's host cores on a
              bounded sample (rank 0, N = 1 only)
 
@@ -218,7 +232,171 @@ def run_reference_arm(args, rank, world):
 
 # ---------------------------------------------------------------------------- GPU arm
 
+def graph_replay_ms(fn, n, stream_dev):
+    """ms per call of `fn` when n calls are captured into one CUDA graph and the replay is timed
+    (the reference times everything this way: triton do_bench_cudagraph, dev/8.11_benchmark_2_kernel.py:52-61)"""
+    fn()
+    torch.cuda.synchronize(stream_dev)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(n):
+            fn()
+    g.replay()
+    torch.cuda.synchronize(stream_dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    g.replay()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / n
+
+
+def cold_l2_ms(fn, flush, stream, reps=10):
+    """median device time of single launches, each preceded by a write of a buffer larger than L2
+    (the flush the reference sketches in dev/test_script.py:325-329); only the launch is timed"""
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn()
+        b.record(stream)
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    return float(np.median(ts))
+
+
+def hbm_roofline(gbs, bytes_alg, peaks, traffic=None):
+    return {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+            "traffic": traffic, "algorithmic_bytes": bytes_alg, "peak_source": peaks["source"],
+            "frac_of_nominal_8TBs": gbs / 8000.0}
+
+
+def leg_prune_compress(dev, stream, peaks):
+    """standalone fused prune+compress (values + reference-layout metadata) through the C ABI"""
+    import ctypes
+    from s24 import _lib
+    L = _lib.lib()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = {}
+    for (n, dtype, scale) in ((PC_M, torch.float16, 1.0), (4096, torch.float16, 1.0), (8192, torch.float16, 1.0),
+                              (32768, torch.float16, 1.0), (PC_M, torch.bfloat16, 0.02)):
+        gp = torch.Generator(device=dev).manual_seed(2000 + n.bit_length() - 1)
+        Ap = torch.empty(n, n, dtype=dtype, device=dev)
+        for r0 in range(0, n, 8192):        # generated in row slabs: a 32768^2 fp32 temporary would be 4 GB
+            Ap[r0:r0 + 8192] = (scale * torch.randn(min(8192, n - r0), n, generator=gp, device=dev, dtype=torch.float32)).to(dtype)
+        pv = torch.empty(n, n // 2, dtype=dtype, device=dev)
+        pe = torch.empty(n // 16, n, dtype=torch.int16, device=dev)
+        code = _lib.FP16 if dtype == torch.float16 else _lib.BF16
+
+        def pc_step():
+            sp = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)   # the capture stream during graph capture
+            _lib.check(L.s24_prune_compress(ctypes.c_void_p(Ap.data_ptr()), n, n, n, code, _lib.MODE_SIGNED,
+                                            _lib.TIE_REFERENCE, ctypes.c_void_p(pv.data_ptr()),
+                                            ctypes.c_void_p(pe.data_ptr()), None, sp))
+
+        for _ in range(5):
+            pc_step()
+        torch.cuda.synchronize(dev)
+        reps = 20 if n >= 16384 else 100
+        ms = time_steps(pc_step, reps, stream) / reps
+        bytes_pc = 3.125 * n * n
+        gbs = bytes_pc / (ms * 1e-3) / 1e9
+        name = f"{'fp16' if dtype == torch.float16 else 'bf16'}_{n}"
+        rec = {"metric": "prune_compress_gbs", "value": gbs, "unit": "GB/s", "ms": ms,
+               "workload": f"fused prune+compress {name.split('_')[0]} {n}x{n} -> values + reference-layout metadata"
+                           + (" (bf16 ~N(0, 0.02): the weight distribution of cfg 5)" if dtype == torch.bfloat16 else ""),
+               "l2": "working set %.0f MB %s the 126 MB L2" % (bytes_pc / 1e6, "fits in" if bytes_pc < 126e6 else "exceeds"),
+               "roofline": hbm_roofline(gbs, bytes_pc, peaks, NCU_DRAM_BYTES_PC_16384 if (n == PC_M and dtype == torch.float16) else None)}
+        if bytes_pc < 300e6:
+            # small enough to live (partly) in L2 and to be launch-bound: also as a CUDA-graph replay and with a cold L2
+            ms_g = graph_replay_ms(pc_step, 50, dev)
+            ms_c = cold_l2_ms(pc_step, flush, stream)
+            rec["graph_replay"] = {"ms": ms_g, "gbs": bytes_pc / (ms_g * 1e-3) / 1e9}
+            rec["cold_l2"] = {"ms": ms_c, "gbs": bytes_pc / (ms_c * 1e-3) / 1e9,
+                              "note": "single launches, each after writing a 256 MiB buffer; event overhead included"}
+        out[name] = rec
+        del Ap, pv, pe
+    del flush
+    return out
+
+
+def leg_cfg5(args, rank, world, dev, stream, barrier):
+    """MLP-shaped product, output columns split over the ranks (strong scaling), three ways"""
+    import torch.distributed as dist
+    import s24
+    from s24.multi import NShardedSpmm
+    M, K, N = 28672, 8192, 65536
+    g = torch.Generator(device=dev).manual_seed(5000)                    # the same W on every rank
+    W = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    for r0 in range(0, M, 7168):
+        W[r0:r0 + 7168] = (0.02 * torch.randn(7168, K, generator=g, device=dev, dtype=torch.float32)).to(torch.bfloat16)
+    vals, _, tc = s24.prune_compress(W, want_ref=False, want_tc=True)    # compressed redundantly, no broadcast
+    del W
+    op = NShardedSpmm(vals, tc)
+    n0, n1 = op.local_columns(N)
+    nl = n1 - n0
+
+    def shard_of(r):
+        gx = torch.Generator(device=dev).manual_seed(5001 + r)
+        return torch.randn(K, nl, generator=gx, device=dev, dtype=torch.float32).to(torch.bfloat16)
+
+    X = shard_of(rank)
+
+    def timed(fn, steps):
+        for _ in range(2):
+            fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        b.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(t.item())
+
+    flops = 2.0 * M * N * K
+    steps = 5
+    ms_shard = timed(lambda: op(X), 10)
+    ms_rep = timed(lambda: op(X, n_total=N, replicated=True, panels=8), steps)
+    ms_fused = timed(lambda: op(X, n_total=N, replicated="fused"), steps)
+    recv = M * N * 2 * (world - 1) // world          # bytes every GPU receives (all-gather) / stores to peers (fused)
+    # ---- untimed: every shard of both replicated results against the product recomputed on this GPU
+    C_gath = op(X, n_total=N, replicated=True, panels=8)
+    C_fused = op(X, n_total=N, replicated="fused")
+    torch.cuda.synchronize(dev)
+    ok_g = ok_f = True
+    for r in range(world):
+        Xr = X if r == rank else shard_of(r)
+        want = s24.spmm(vals, tc, Xr)                                                   # library's default tile
+        want_f = s24.spmm(vals, tc, Xr, manual_config={"BM": 256, "BN": 256})           # the scatter kernel's tile
+        ok_g = ok_g and torch.equal(C_gath[:, r * nl:(r + 1) * nl], want)
+        ok_f = ok_f and torch.equal(C_fused[:, r * nl:(r + 1) * nl], want_f)
+        del want, want_f
+    flags = torch.tensor([int(ok_g), int(ok_f)], device=dev, dtype=torch.int32)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    del C_gath, C_fused
+    op.close()
+    return {
+        "workload": f"W24 {M}x{K} bf16 (2:4, ~N(0, 0.02)) . X {K}x{N} bf16, output columns split over {world} GPUs",
+        "scaling": "strong",
+        "sharded": {"ms": ms_shard, "tflops": flops / ms_shard / 1e9, "collective": "none"},
+        "replicated_allgather": {"ms": ms_rep, "tflops": flops / ms_rep / 1e9, "received_bytes_per_gpu": recv,
+                                 "gbs_per_gpu": recv / (ms_rep * 1e-3) / 1e9,
+                                 "how": "GEMM in 8 row panels, NCCL all_gather_into_tensor + shard re-layout kernel per panel on a side stream",
+                                 "equals_recomputed_shards": bool(flags[0].item())},
+        "replicated_fused": {"ms": ms_fused, "tflops": flops / ms_fused / 1e9, "stored_to_peers_bytes_per_gpu": recv,
+                             "gbs_per_gpu": recv / (ms_fused * 1e-3) / 1e9, "frac_of_peer_copy_770gbs": recv / (ms_fused * 1e-3) / 1e9 / 770.0,
+                             "how": "one kernel: the GEMM epilogue stores each tile into every rank's peer-mapped copy of C (bulk stores over NVLink)",
+                             "equals_recomputed_shards": bool(flags[1].item())},
+    }
+
+
 def run_ours(args, rank, world, local):
+    import datetime
     import s24
     from s24 import _lib
     import gluon_ws_sparse
@@ -230,9 +408,10 @@ def run_ours(args, rank, world, local):
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     stream = torch.cuda.current_stream(dev)
     peaks = measured_peaks()
+    warmup = max(args.warmup, 3)
 
     # ---- inputs (seeded, N(0,1) like every reference benchmark: 8.11_benchmark_2_kernel.py:67-68)
     g = torch.Generator(device=dev).manual_seed(4000)
@@ -241,7 +420,6 @@ def run_ours(args, rank, world, local):
     B = torch.randn(GEMM_K, GEMM_N, generator=gb, device=dev, dtype=torch.float32).to(torch.float16)
     vals, E, tc = s24.prune_compress(A, want_ref=True, want_tc=True)
     C = torch.empty(GEMM_M, GEMM_N, dtype=torch.float16, device=dev)
-    del A
 
     from s24.multi import NShardedSpmm
     op = NShardedSpmm(vals, tc, spmm_fn=lambda v, m, b, out=None: s24.spmm(v, m, b, out=C if out is None else out))
@@ -254,7 +432,18 @@ def run_ours(args, rank, world, local):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(max(args.warmup, 3)):
+    def max_over_ranks(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if use_dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def check_status(where):
+        if _lib.lib().s24_device_status(None) != 0:
+            raise SystemExit(f"device status after {where}: {_lib.last_error()}")
+
+    # ---- headline: K steps, barrier + synchronize on both sides, max over ranks
+    for _ in range(warmup):
         gemm_step()
     barrier()
     sampler = ClockSampler(local)
@@ -266,18 +455,51 @@ def run_ours(args, rank, world, local):
     ms = time_steps(gemm_step, args.steps, stream)
     sampler.mark()
     barrier()
-    rc = _lib.lib().s24_device_status(None)
-    if rc != 0:
-        raise SystemExit(f"device status after the timed region: {_lib.last_error()}")
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if use_dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    ms_per_step = ms_max / args.steps
-    flops_per_step = 2.0 * GEMM_M * GEMM_N * GEMM_K * world
+    check_status("the timed region")
+    ms_per_step = max_over_ranks(ms) / args.steps
+    flops_gemm = 2.0 * GEMM_M * GEMM_N * GEMM_K
+    flops_per_step = flops_gemm * world
     value = flops_per_step / (ms_per_step * 1e-3) / 1e12
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- sustained: the same launch back to back for two seconds (power-capped clocks), sampler inside
+    sampler2 = ClockSampler(local)
+    if rank == 0:
+        sampler2.start()
+        time.sleep(0.1)
+    barrier()
+    sampler2.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin, n_sus = time.time(), 0
+    e0.record(stream)
+    while time.time() - t_begin < 2.0:
+        for _ in range(100):
+            gemm_step()
+        n_sus += 100
+        torch.cuda.synchronize(dev)            # keeps the launch queue short; a few microseconds per 45 ms
+    e1.record(stream)
+    e1.synchronize()
+    sampler2.mark()
+    ms_sus = max_over_ranks(e0.elapsed_time(e1) / n_sus)
+    barrier()
+    check_status("the sustained loop")
+    sustained = None
+    if rank == 0:
+        c2 = sampler2.stop()
+        tf = flops_gemm / (ms_sus * 1e-3) / 1e12
+        sustained = {"ms_per_step": ms_sus, "steps": n_sus, "tflops_per_gpu": tf,
+                     "frac_of_2x_sustained_dense": tf / (2.0 * peaks["bf16_tflops_sustained"]),
+                     "peak": 2.0 * peaks["bf16_tflops_sustained"], "peak_source": peaks["source"],
+                     "sm_mhz_median": c2.get("sm_mhz"), "sm_mhz_min": c2.get("sm_min_mhz"),
+                     "cycles_per_step": (ms_sus * 1e-3 * c2["sm_mhz"] * 1e6) if c2.get("sm_mhz") else None,
+                     "power_w_max": c2.get("power_w_max"), "reasons": c2.get("reasons"),
+                     "samples_in_timed_region": c2.get("samples_in_timed_region")}
 
     # ---- end to end through the reference-facing call with host buffers (every rank, max over ranks)
+    try:
+        affinity = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        affinity = []
     h_vals = vals.cpu().pin_memory()
     h_E = E.cpu().pin_memory()
     h_B = B.cpu().pin_memory()
@@ -288,92 +510,153 @@ def run_ours(args, rank, world, local):
     NBUF = 2
     d_in = [(torch.empty_like(vals), torch.empty_like(E), torch.empty_like(B)) for _ in range(NBUF)]
     d_out = [None] * NBUF
+    d_fixed = torch.empty_like(C)
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     ev_in = [torch.cuda.Event() for _ in range(NBUF)]        # inputs of buffer i are on the device
     ev_free = [torch.cuda.Event() for _ in range(NBUF)]      # buffer i's inputs were consumed
     ev_done = [torch.cuda.Event() for _ in range(NBUF)]      # result of buffer i is ready
     ev_down = [torch.cuda.Event() for _ in range(NBUF)]      # result of buffer i is on the host
 
-    def e2e_run(steps):
+    def e2e_run(steps, compute=True, marks=None):
         for i in range(steps):
             b = i % NBUF
             with torch.cuda.stream(s_in):
                 if i >= NBUF:
                     s_in.wait_event(ev_free[b])
+                if marks is not None and i == 0:
+                    marks["in0"].record(s_in)
                 d_in[b][0].copy_(h_vals, non_blocking=True)
                 d_in[b][1].copy_(h_E, non_blocking=True)
                 d_in[b][2].copy_(h_B, non_blocking=True)
                 ev_in[b].record(s_in)
+                if marks is not None and i == steps - 1:
+                    marks["in1"].record(s_in)
             stream.wait_event(ev_in[b])
             if i >= NBUF:
                 stream.wait_event(ev_down[b])                # the previous result in this slot has left
-            d_out[b] = gluon_ws_sparse.run_sparse_ws_matmul(*d_in[b], tune=False)   # tile by the library's heuristic
+            if compute:
+                d_out[b] = gluon_ws_sparse.run_sparse_ws_matmul(*d_in[b], tune=False)   # tile by the library's heuristic
+            else:
+                d_out[b] = d_fixed                           # copies-only pass: nothing is computed
             ev_free[b].record(stream)
             ev_done[b].record(stream)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_done[b])
+                if marks is not None and i == 0:
+                    marks["out0"].record(s_out)
                 h_C.copy_(d_out[b], non_blocking=True)
                 d_out[b].record_stream(s_out)
                 ev_down[b].record(s_out)
+                if marks is not None and i == steps - 1:
+                    marks["out1"].record(s_out)
         stream.wait_event(ev_down[(steps - 1) % NBUF])
         if steps > 1:
             stream.wait_event(ev_down[(steps - 2) % NBUF])
 
+    def e2e_timed(steps, compute, marks=None):
+        barrier()
+        e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_in.wait_stream(stream)
+        s_out.wait_stream(stream)
+        e_start.record(stream)
+        s_in.wait_event(e_start)
+        e2e_run(steps, compute, marks)
+        e_stop.record(stream)
+        e_stop.synchronize()
+        torch.cuda.synchronize(dev)
+        return e_start.elapsed_time(e_stop)
+
     # enough steps that filling and draining the three-stage pipeline (one H2D + one GEMM + one D2H,
     # about 7 ms) is a small part of the timed region
     e2e_steps = max(4, min(args.steps, 50))
-    e2e_run(3)
-    barrier()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s_in.wait_stream(stream)
-    s_out.wait_stream(stream)
-    e_start.record(stream)
-    s_in.wait_event(e_start)
-    e2e_run(e2e_steps)
-    e_stop.record(stream)
-    e_stop.synchronize()
-    ms_e2e = e_start.elapsed_time(e_stop)
-    barrier()
-    t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
-    if use_dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = flops_per_step / (float(t.item()) / e2e_steps * 1e-3) / 1e12
     h2d = (h_vals.numel() + h_B.numel()) * 2 + h_E.numel() * 2
     d2h = h_C.numel() * 2
+    e2e_run(3)
+    ms_e2e_rank = e2e_timed(e2e_steps, True)
+    e2e_value = flops_per_step / (max_over_ranks(ms_e2e_rank) / e2e_steps * 1e-3) / 1e12
+    check_status("the end-to-end region")
+    # copies only (no GEMM): what the host link allows at this number of GPUs, and each direction's own rate
+    marks = {k: torch.cuda.Event(enable_timing=True) for k in ("in0", "in1", "out0", "out1")}
+    ms_copy_rank = e2e_timed(e2e_steps, False, marks)
+    h2d_gbs = h2d * e2e_steps / (marks["in0"].elapsed_time(marks["in1"]) * 1e-3) / 1e9
+    d2h_gbs = d2h * e2e_steps / (marks["out0"].elapsed_time(marks["out1"]) * 1e-3) / 1e9
+    per_rank = torch.tensor([ms_e2e_rank / e2e_steps, ms_copy_rank / e2e_steps, h2d_gbs, d2h_gbs,
+                             float(len(affinity)), float(affinity[0] if affinity else -1), float(affinity[-1] if affinity else -1)],
+                            device=dev, dtype=torch.float64)
+    if use_dist:
+        allr = [torch.empty_like(per_rank) for _ in range(world)]
+        dist.all_gather(allr, per_rank)
+    else:
+        allr = [per_rank]
+    copy_ceiling = flops_per_step / (max_over_ranks(ms_copy_rank) / e2e_steps * 1e-3) / 1e12
+    e2e_ranks = [{"rank": i, "ms_per_step": float(t[0]), "copies_only_ms_per_step": float(t[1]), "h2d_gbs": float(t[2]),
+                  "d2h_gbs": float(t[3]), "cpus_allowed": int(t[4]), "cpu_first": int(t[5]), "cpu_last": int(t[6])}
+                 for i, t in enumerate(allr)]
+    del h_vals, h_E, h_B, h_C, d_in, d_out, d_fixed
+
+    # ---- cfg 5 (only with several GPUs): the paths that do communicate
+    cfg5 = None
+    if use_dist:
+        del A
+        cfg5 = leg_cfg5(args, rank, world, dev, stream, barrier)
+        check_status("the cfg5 leg")
+
+    # ---- single-GPU legs (rank 0 of a one-GPU run): the reference's other headline lines
+    extra = {}
+    pc_all = None
     if rank == 0:
-        clocks = sampler.stop()
-    del h_vals, h_E, h_B, h_C, d_in, d_out
+        pc_all = leg_prune_compress(dev, stream, peaks)
+    if rank == 0 and world == 1:
+        import importlib.util
 
-    # ---- standalone prune+compress bandwidth (rank 0 reports its own GPU)
-    pc = None
-    if rank == 0:
-        gp = torch.Generator(device=dev).manual_seed(2014)
-        Ap = torch.randn(PC_M, PC_K, generator=gp, device=dev, dtype=torch.float32).to(torch.float16)
-        pv = torch.empty(PC_M, PC_K // 2, dtype=torch.float16, device=dev)
-        pe = torch.empty(PC_M // 16, PC_K, dtype=torch.int16, device=dev)
-        L = _lib.lib()
-        import ctypes
-        sp = ctypes.c_void_p(stream.cuda_stream)
+        def dropin(rel):
+            spec = importlib.util.spec_from_file_location("dropin_" + Path(rel).stem.replace(".", "_"), PKG / "compression" / rel)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            return mod
 
-        def pc_step():
-            _lib.check(L.s24_prune_compress(ctypes.c_void_p(Ap.data_ptr()), PC_M, PC_K, PC_K, _lib.FP16,
-                                            _lib.MODE_SIGNED, _lib.TIE_REFERENCE, ctypes.c_void_p(pv.data_ptr()),
-                                            ctypes.c_void_p(pe.data_ptr()), None, sp))
+        two = dropin("kernels/11.1_2_kernel_baseline.py")
+        n_leg = 50
 
-        for _ in range(5):
-            pc_step()
-        torch.cuda.synchronize(dev)
-        pc_steps = 20
-        ms_pc = time_steps(pc_step, pc_steps, stream) / pc_steps
-        bytes_pc = 3.125 * PC_M * PC_K
-        gbs = bytes_pc / (ms_pc * 1e-3) / 1e9
-        pc = {"metric": "prune_compress_gbs", "value": gbs, "unit": "GB/s", "ms": ms_pc,
-              "workload": f"fused prune+compress fp16 {PC_M}x{PC_K} -> values + reference-layout metadata",
-              "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                           "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PC_16384,
-                           "algorithmic_bytes": bytes_pc, "peak_source": peaks["source"],
-                           "frac_of_nominal_8TBs": gbs / 8000.0}}
-        del Ap, pv, pe
+        def med3(fn):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize(dev)
+            return float(np.median([time_steps(fn, n_leg, stream) / n_leg for _ in range(3)]))
+
+        # cfg 3 at 8192^3: dense A -> prune+compress kernel -> sparse GEMM, both launches timed
+        ms_two = med3(lambda: two.run_2_kernel_ws_matmul(A, B, tune=False))
+        extra["two_kernel"] = {"ms": ms_two, "tflops": flops_gemm / ms_two / 1e9, "launches_per_step": 2,
+                               "workload": "run_2_kernel_ws_matmul(A, B) at M=K=N=8192 fp16: prune+compress kernel then sparse GEMM",
+                               "reference_h100_tflops": 933.96}
+        # cfg 4 at 8192^3: pruning epilogue vs the plain GEMM on the same tile, one after the other
+        fo = {}
+        for name, cfg in (("512x224", {"BM": 512, "BN": 224}), ("256x256", {"BM": 256, "BN": 256})):
+            ms_plain = med3(lambda: s24.spmm(vals, tc, B, out=C, manual_config=cfg))
+            ms_fo = med3(lambda: s24.spmm_prune_out(vals, tc, B, want_ref=True, want_tc=False, manual_config=cfg))
+            fo[name] = {"ms": ms_fo, "tflops": flops_gemm / ms_fo / 1e9, "precompressed_ms": ms_plain,
+                        "precompressed_tflops": flops_gemm / ms_plain / 1e9, "ratio_to_precompressed": ms_plain / ms_fo}
+        best = max(fo, key=lambda k: fo[k]["tflops"])
+        extra["fused_out"] = {"workload": "s24_spmm_prune_out at M=K=N=8192 fp16 (C stored as values + reference-layout metadata)",
+                              "tile": best, **fo[best], "tiles": fo, "reference_h100_ratio": 0.98}
+        check_status("the two-kernel / fused-output legs")
+        # cfg 1: the reference's CPU-runnable case; operands + output (68 MB) fit in L2, so warm and cold differ
+        g1 = torch.Generator(device=dev).manual_seed(1234)
+        A1 = torch.randn(2048, 2048, generator=g1, device=dev, dtype=torch.float32).to(torch.float16)
+        B1 = torch.randn(2048, 8192, generator=g1, device=dev, dtype=torch.float32).to(torch.float16)
+        v1, _, tc1 = s24.prune_compress(A1, want_ref=False, want_tc=True)
+        C1 = torch.empty(2048, 8192, dtype=torch.float16, device=dev)
+        fl1 = 2.0 * 2048 * 2048 * 8192
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        step1 = lambda: s24.spmm(v1, tc1, B1, out=C1)  # noqa: E731
+        ms_w = med3(step1)
+        ms_g = graph_replay_ms(step1, 50, dev)
+        ms_c = cold_l2_ms(step1, flush, stream)
+        extra["cfg1"] = {"workload": "sparse GEMM 2048 x 2048 (2:4) x 2048 x 8192 fp16",
+                         "warm": {"ms": ms_w, "tflops": fl1 / ms_w / 1e9}, "graph_replay": {"ms": ms_g, "tflops": fl1 / ms_g / 1e9},
+                         "cold_l2": {"ms": ms_c, "tflops": fl1 / ms_c / 1e9,
+                                     "note": "single launches, each after writing a 256 MiB buffer; event overhead included"}}
+        del A1, B1, v1, tc1, C1, flush
 
     # ---- CPU baseline (rank 0, single GPU run only; bounded sample)
     cpu = None
@@ -381,15 +664,17 @@ def run_ours(args, rank, world, local):
         threads = os.cpu_count() or 1
         rows = 512
         step = cpu_reference_sample(rows, threads)
-        step()
-        reps, t_pc, t_mm = 3, 0.0, 0.0
+        for _ in range(3):
+            step()
+        reps, t_pc, t_mm = 20, [], []
         for _ in range(reps):
             a, b, _ = step()
-            t_pc += a / reps
-            t_mm += b / reps
+            t_pc.append(a)
+            t_mm.append(b)
+        t_pc, t_mm = float(np.median(t_pc)), float(np.median(t_mm))
         cpu = {"value": 2.0 * rows * GEMM_N * GEMM_K / t_mm / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                "sample": f"first {rows} of {GEMM_M} rows of A against the full B: C-port prune+compress then torch fp32 "
-                         f"CPU matmul (matmul time in value)",
+                         f"CPU matmul (matmul time in value; median of {reps} repeats)",
                "prune_compress_gbs": 3.125 * rows * GEMM_K / t_pc / 1e9}
 
     if rank == 0:
@@ -397,7 +682,7 @@ def run_ours(args, rank, world, local):
         per_gpu = value / world
         line = {
             "metric": "sparse_gemm_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": value / world / H100_PRECOMPRESSED_SPARSE_8192 if world == 1 else None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"sparse GEMM M=K=N={GEMM_M} fp16, A 2:4 pre-compressed, fp32 accumulate, fp16 out; "
@@ -408,16 +693,25 @@ def run_ours(args, rank, world, local):
                        "baseline_note": "vs_baseline divides by the reference's published H100 number (1015.48 TFLOP/s)"},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": sparse_peak, "unit": "TFLOP/s",
                          "frac": per_gpu / sparse_peak, "traffic": NCU_DRAM_BYTES_GEMM_8192,
-                         "algorithmic_flops": 2.0 * GEMM_M * GEMM_N * GEMM_K, "peak_source": peaks["source"],
-                         "peak_note": "2 x measured dense bf16 burst peak (2:4 sparse issues half the MACs)",
-                         "frac_of_sustained": per_gpu / (2.0 * peaks["bf16_tflops_sustained"])},
+                         "algorithmic_flops": flops_gemm, "peak_source": peaks["source"],
+                         "peak_note": "2 x measured dense bf16 burst peak (2:4 sparse issues half the MACs); the timed region "
+                                      "is a burst of a few milliseconds, see `sustained` for the power-capped figure"},
+            "sustained": sustained,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "call": "run_sparse_ws_matmul(A_vals, E, B) with pinned host buffers, H2D / compute / D2H double-buffered on three streams"},
+                    "call": "run_sparse_ws_matmul(A_vals, E, B) with pinned host buffers, H2D / compute / D2H double-buffered on three streams",
+                    "copies_only_value": copy_ceiling,
+                    "copies_only_note": "the same pipeline with the GEMM left out: what the host link allows at this number of GPUs",
+                    "ranks": e2e_ranks},
+            # per timed step one sparse GEMM launch per GPU (the e2e region adds one metadata re-layout launch per step)
             "gpu_launches": args.steps * world,
             "clocks": clocks,
         }
-        if pc is not None:
-            line["prune_compress"] = pc
+        if pc_all is not None:
+            line["prune_compress"] = pc_all.pop(f"fp16_{PC_M}")
+            line["prune_compress_sizes"] = pc_all
+        line.update(extra)
+        if cfg5 is not None:
+            line["cfg5"] = cfg5
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

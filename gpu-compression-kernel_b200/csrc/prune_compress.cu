@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) prune_compress_kernel(const PcParams p)
 // ---------------------------------------------------------------- dense prune (prune_2_4)
 
 template <int DT, int MODE, bool V128>
-__global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* __restrict__ A, uint16_t* __restrict__ out,
+__global__ void __launch_bounds__(256) prune_dense_kernel(const uint16_t* A, uint16_t* out,   // out may alias A (in-place prune): no __restrict__
                                                           int64_t numel, int tie)
 {
     const int64_t total = (int64_t)gridDim.x * blockDim.x;
@@ -250,6 +250,12 @@ static int launch_prune_compress(const void* A, int64_t M, int64_t K, int64_t ld
     if (!aligned(A, 16) || !aligned(vals, 16) || !aligned(meta_ref, 16) || !aligned(meta_tc, 16))
         return fail(S24_ERR_INVALID_ARG, "prune_compress: pointers must be 16-byte aligned");
     if (M == 0 || K == 0) return S24_OK;
+    if (meta_tc != nullptr && (M % 128 != 0 || K % 128 != 0)) {
+        // tensor-core records are whole (128 x 128) units; the kernel writes only the words of rows
+        // < M and columns < K, the rest get a valid code here (the values they index read as zero)
+        int rc = check_cuda(cudaMemsetAsync(meta_tc, 0x44, s24_meta_tc_bytes(M, K), stream), "metadata prefill");
+        if (rc) return rc;
+    }
 
     PcParams p;
     p.A = static_cast<const uint16_t*>(A);
@@ -358,6 +364,12 @@ extern "C" int s24_meta_convert(const void* src, int from_layout, void* dst, int
         return fail(S24_ERR_SHAPE, "meta_convert: needs M %% 32 == 0 and K %% 64 == 0 (got %lld x %lld)", (long long)M, (long long)K);
     if (!aligned(src, 4) || !aligned(dst, 4)) return fail(S24_ERR_INVALID_ARG, "meta_convert: pointers must be 4-byte aligned");
     if (M == 0 || K == 0) return S24_OK;
+    if (to_layout == S24_META_TC && (M % 128 != 0 || K % 128 != 0)) {
+        // words of partly covered records that lie outside the matrix: a valid code (see s24_prune_compress)
+        int rc = check_cuda(cudaMemsetAsync(dst, 0x44, s24_meta_tc_bytes(M, K), static_cast<cudaStream_t>(stream)),
+                            "metadata prefill");
+        if (rc) return rc;
+    }
     const int64_t ncols = K / 16;
     const int64_t pairs = (M / 2) * ncols;
     const int64_t blocks = (pairs + 255) / 256;

@@ -2,8 +2,9 @@
 // GEMM uses: mbarriers, TMA tensor loads, tensor memory (TMEM) management, tcgen05.cp /
 // tcgen05.mma.sp / tcgen05.commit / tcgen05.ld, cluster addressing.
 //
-// Every wait is bounded: mbar_wait() gives up after kWaitTimeoutNs and reports false, so a
-// protocol error shows up as a status word the host can read, never as a hung GPU.
+// Every wait is bounded: mbar_wait() gives up after its limit (kWaitTimeoutNs unless the caller
+// passes another) and reports false, so a protocol error shows up as a status word the host can
+// read, never as a hung GPU.
 #pragma once
 
 #include <cuda.h>
@@ -109,7 +110,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // bounded wait; false = timed out (the caller sets the status word and unwinds)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns = kWaitTimeoutNs)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
@@ -117,7 +118,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer() - t0 > kWaitTimeoutNs) return false;
+        if (globaltimer() - t0 > limit_ns) return false;
     }
 }
 

@@ -29,6 +29,10 @@ struct GemmParams {
     // all with row stride ldc; unused by the other kernels
     void* dst[8];
     int n_dst;
+    // limit of every barrier wait in nanoseconds, and (self-test only, 0 = off) the number of
+    // k-blocks after which the producer stops loading so that the other roles' waits run out
+    unsigned long long wait_limit_ns;
+    int selftest_stop_after_kblocks;
 };
 
 __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code)

@@ -36,6 +36,13 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
+#ifndef S24_B_TAIL_BOX
+#define S24_B_TAIL_BOX 1
+#endif
+#ifndef S24_EARLY_RELEASE
+#define S24_EARLY_RELEASE 1
+#endif
+
 namespace s24 {
 
 using namespace ptx;
@@ -71,7 +78,11 @@ struct GemmCfg {
     static constexpr int kBAtoms = (kBNCta + 63) / 64;          // loaded as whole 64-column atoms
     static constexpr int kBBytes = kBAtoms * kBAtomBytes;      // shared-memory footprint of a B stage
     static constexpr int kBtAtomBytes = kBNCta * 128;           // transposed B: N rows x 64 k-values x 2 B
-    static constexpr int kBLoadBytes = BT ? 2 * kBtAtomBytes : kBBytes;   // bytes the copies deliver
+    // columns of the last atom that belong to this CTA: loaded with a narrower box of its own so
+    // that no column outside the tile is fetched (0 = the last atom is whole)
+    static constexpr int kBTailCols = S24_B_TAIL_BOX ? (kBNCta % 64) : 0;
+    static constexpr int kBLoadBytes = BT ? 2 * kBtAtomBytes
+                                          : (kBTailCols ? (kBAtoms - 1) * kBAtomBytes + kBlockK * kBTailCols * 2 : kBBytes);
     static constexpr int kESubBytes = 2048;
     static constexpr int kEBytes = MT * kESubBytes;
     static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;
@@ -104,7 +115,7 @@ __device__ __forceinline__ uint32_t prune_group_f32(float a0, float a1, float a2
 template <class Cfg>
 __global__ void __launch_bounds__(kThreads, 1)
 spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-            const __grid_constant__ CUtensorMap tm_e, const GemmParams p)
+            const __grid_constant__ CUtensorMap tm_b_tail, const __grid_constant__ CUtensorMap tm_e, const GemmParams p)
 {
     constexpr int G = Cfg::kG;
     constexpr int BN = Cfg::kBN;
@@ -170,14 +181,20 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (elect_one()) {
             int s = 0;
             uint32_t phase = 0;
-            for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
+            bool stopped = false;
+            for (int t = unit; t < num_tiles && !stopped && !*abort_flag; t += num_units) {
                 int tm, tn;
                 tile_coords(t, num_m, num_n, tm, tn);
                 // sub-tile m of this CTA: rows row0 + m * 128 * G .. + 127
                 const int row0 = tm * Cfg::kTileRows + (int)cta_rank * kRowsPerCta;
                 const int col0 = tn * BN + (int)cta_rank * Cfg::kBNCta;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u)) {
+                    // self-test of the time-out path: stop feeding the ring; nothing is left in flight
+                    if (p.selftest_stop_after_kblocks > 0 && kb >= p.selftest_stop_after_kblocks) {
+                        stopped = true;
+                        break;
+                    }
+                    if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u, p.wait_limit_ns)) {
                         report_timeout(p.status, abort_flag, 1);
                         break;
                     }
@@ -212,8 +229,11 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (int i = 0; i < Cfg::kBAtoms; ++i) {
-                            if (G == 2) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
-                            else tma_load_2d(b_dst + i * Cfg::kBAtomBytes, &tm_b, col0 + 64 * i, kb * kBlockK, full);
+                            // the last atom of a tile whose width is not a multiple of 64 comes through
+                            // the narrower box: same 128-byte swizzled rows, only the tile's own columns
+                            const CUtensorMap* map = (Cfg::kBTailCols != 0 && i == Cfg::kBAtoms - 1) ? &tm_b_tail : &tm_b;
+                            if (G == 2) tma_load_2d_pair(b_dst + i * Cfg::kBAtomBytes, map, col0 + 64 * i, kb * kBlockK, full);
+                            else tma_load_2d(b_dst + i * Cfg::kBAtomBytes, map, col0 + 64 * i, kb * kBlockK, full);
                         }
                     }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
@@ -227,7 +247,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             int s = 0, a = 0;
             uint32_t phase = 0, acc_phase = 0;
             for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
-                if (!mbar_wait(bar_acc_empty + 8 * a, acc_phase ^ 1u)) {
+                if (!mbar_wait(bar_acc_empty + 8 * a, acc_phase ^ 1u, p.wait_limit_ns)) {
                     report_timeout(p.status, abort_flag, 3);
                     break;
                 }
@@ -235,7 +255,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const uint32_t tmem_d = tmem_base + (uint32_t)(a * Cfg::kAccCols);
                 bool ok = true;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(bar_full + 8 * s, phase)) {
+                    if (!mbar_wait(bar_full + 8 * s, phase, p.wait_limit_ns)) {
                         report_timeout(p.status, abort_flag, 2);
                         ok = false;
                         break;
@@ -292,7 +312,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
             int tm, tn;
             tile_coords(t, num_m, num_n, tm, tn);
-            if (!mbar_wait(bar_acc_full + 8 * a, acc_phase)) {
+            if (!mbar_wait(bar_acc_full + 8 * a, acc_phase, p.wait_limit_ns)) {
                 if (lane == 0) report_timeout(p.status, abort_flag, 4);
                 break;
             }
@@ -331,14 +351,68 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 bulk_commit();
             } else if constexpr (!Cfg::kPruneOut) {
-                // Drain in as few round trips as possible: one tcgen05.ld per 128 (then 64, then 32)
-                // columns, convert, and hand each 8-column group to the store unit right away, so
-                // only the load round trips (not the stores) stand between the MMA warp and its
-                // accumulator.
+                // Drain in as few round trips as possible: one tcgen05.ld per 128 (then 64 + 32)
+                // columns, round to 16 bits in registers, hand tensor memory back to the MMA warp and
+                // only then issue the stores (32 bytes per thread to rows that lie ldc apart, which
+                // the load/store unit takes a sector at a time): the next tile's main loop starts
+                // while this tile is still on its way to memory.
                 uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
                 const bool row_ok = row < p.M;
                 // 16 columns = 32 bytes = one full L2 sector per store when C allows it
                 const bool wide = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * 2)) & 31u) == 0;
+                auto store16 = [&](const uint32_t* q, int c) {   // 16 columns starting at tile column c
+                    if (!row_ok) return;
+                    if (wide && col0 + c + 16 <= p.N) {
+                        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(crow + c), "r"(q[0]), "r"(q[1]),
+                                     "r"(q[2]), "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7])
+                                     : "memory");
+                    } else {
+                        if (col0 + c < p.N) *reinterpret_cast<uint4*>(crow + c) = make_uint4(q[0], q[1], q[2], q[3]);
+                        if (col0 + c + 8 < p.N) *reinterpret_cast<uint4*>(crow + c + 8) = make_uint4(q[4], q[5], q[6], q[7]);
+                    }
+                };
+                static_assert(CW % 32 == 0, "epilogue works in 32-column pieces");
+#if S24_EARLY_RELEASE
+                uint32_t q[CW / 2];
+                auto pack = [&](const uint32_t* r, int c_off, int width) {
+#pragma unroll
+                    for (int j = 0; j < width / 2; ++j)
+                        q[c_off / 2 + j] = pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), p.bf16);
+                };
+                int done = 0;
+#pragma unroll
+                for (int k = 0; k < CW / 128; ++k) {
+                    uint32_t r[128];
+                    tc_ld_32x32b_x128(tacc + (uint32_t)done, r);
+                    tc_wait_ld();
+                    pack(r, done, 128);
+                    done += 128;
+                }
+                if constexpr ((CW % 128) == 96) {
+                    uint32_t r[64], r2[32];
+                    tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
+                    tc_ld_32x32b_x32(tacc + (uint32_t)(done + 64), r2);
+                    tc_wait_ld();
+                    pack(r, done, 64);
+                    pack(r2, done + 64, 32);
+                } else if constexpr ((CW % 128) == 64) {
+                    uint32_t r[64];
+                    tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
+                    tc_wait_ld();
+                    pack(r, done, 64);
+                } else if constexpr ((CW % 128) == 32) {
+                    uint32_t r[32];
+                    tc_ld_32x32b_x32(tacc + (uint32_t)done, r);
+                    tc_wait_ld();
+                    pack(r, done, 32);
+                }
+                // every accumulator column of this warp has been read: hand TMEM back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+#pragma unroll
+                for (int i = 0; i < CW / 16; ++i) store16(q + 8 * i, 16 * i);
+#else
                 auto emit = [&](const uint32_t* r, int c_off, int width) {
 #pragma unroll
                     for (int i = 0; i < width / 16; ++i) {
@@ -346,16 +420,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             q[j] = pack2(__uint_as_float(r[16 * i + 2 * j]), __uint_as_float(r[16 * i + 2 * j + 1]), p.bf16);
-                        const int c = c_off + 16 * i;
-                        if (!row_ok) continue;
-                        if (wide && col0 + c + 16 <= p.N) {
-                            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(crow + c), "r"(q[0]), "r"(q[1]),
-                                         "r"(q[2]), "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7])
-                                         : "memory");
-                        } else {
-                            if (col0 + c < p.N) *reinterpret_cast<uint4*>(crow + c) = make_uint4(q[0], q[1], q[2], q[3]);
-                            if (col0 + c + 8 < p.N) *reinterpret_cast<uint4*>(crow + c + 8) = make_uint4(q[4], q[5], q[6], q[7]);
-                        }
+                        store16(q, c_off + 16 * i);
                     }
                 };
                 int done = 0;
@@ -381,11 +446,10 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     emit(r, done, 32);
                     done += 32;
                 }
-                static_assert(CW % 32 == 0, "epilogue works in 32-column pieces");
-                // every accumulator column of this warp has been read: hand TMEM back to the MMA warp
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+#endif
             } else {
                 // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
                 constexpr int NCH = CW / 32;     // 32-column chunks of this warp
@@ -535,7 +599,7 @@ struct GemmArgs {
 template <class Cfg>
 static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
 {
-    CUtensorMap tm_a, tm_b, tm_e;
+    CUtensorMap tm_a, tm_b, tm_b_tail, tm_e;
     const CUtensorMapDataType dt = g.dtype == S24_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     int rc = make_map_2d(&tm_a, dt, 2, g.vals, (uint64_t)(g.K / 2), (uint64_t)g.M, (uint64_t)g.K, 64, kRowsPerCta,
                          CU_TENSOR_MAP_SWIZZLE_128B, "A values");
@@ -547,6 +611,12 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
         rc = make_map_2d(&tm_b, dt, 2, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, 64, kBlockK,
                          CU_TENSOR_MAP_SWIZZLE_128B, "B");
     if (rc) return rc;
+    tm_b_tail = tm_b;
+    if (!Cfg::kBT && Cfg::kBTailCols != 0) {
+        rc = make_map_2d(&tm_b_tail, dt, 2, g.B, (uint64_t)g.N, (uint64_t)g.K, (uint64_t)g.ldb * 2, Cfg::kBTailCols, kBlockK,
+                         CU_TENSOR_MAP_SWIZZLE_128B, "B (last atom)");
+        if (rc) return rc;
+    }
     const uint64_t records = (uint64_t)((g.M + 127) / 128) * (uint64_t)((g.K + 127) / 128);
     rc = make_map_2d(&tm_e, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, g.meta_tc, 128, records * 4, 512, 128, 4,
                      CU_TENSOR_MAP_SWIZZLE_NONE, "metadata");
@@ -584,7 +654,7 @@ static int launch_cfg(const GemmArgs& g, cudaStream_t stream)
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&lc, spmm_kernel<Cfg>, tm_a, tm_b, tm_e, g.p), "sparse GEMM launch");
+    return check_cuda(cudaLaunchKernelEx(&lc, spmm_kernel<Cfg>, tm_a, tm_b, tm_b_tail, tm_e, g.p), "sparse GEMM launch");
 }
 
 int* status_word_address()
@@ -604,7 +674,8 @@ int* status_word_address()
 static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                     int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg, cudaStream_t stream,
                     bool prune_out = false, void* c_vals = nullptr, void* c_meta_ref = nullptr, void* c_meta_tc = nullptr,
-                    bool bt = false, void* const* dsts = nullptr, int n_dst = 0)
+                    bool bt = false, void* const* dsts = nullptr, int n_dst = 0, unsigned long long wait_limit_ns = kWaitTimeoutNs,
+                    int selftest_stop_after_kblocks = 0)
 {
     const char* who = prune_out ? "spmm_prune_out" : (bt ? "spmm_bt" : (dsts ? "spmm_scatter" : "spmm"));
     if (dsts != nullptr) {
@@ -655,9 +726,16 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.c_vals = c_vals;
     g.p.c_meta_ref = static_cast<uint32_t*>(c_meta_ref);
     g.p.c_meta_tc = static_cast<uint32_t*>(c_meta_tc);
+    g.p.wait_limit_ns = wait_limit_ns;
+    g.p.selftest_stop_after_kblocks = selftest_stop_after_kblocks;
     g.p.n_dst = dsts ? n_dst : 0;
     for (int d = 0; d < 8; ++d) g.p.dst[d] = (dsts && d < n_dst) ? dsts[d] : nullptr;
     if (dsts != nullptr) return launch_cfg<GemmCfg<2, 256, 3, false, 1, false, true>>(g, stream);
+    if (prune_out && c_meta_tc != nullptr && M % 128 != 0) {
+        // the last 128-row record group is only partly written by the epilogue: give the rest a valid code
+        int rc = check_cuda(cudaMemsetAsync(c_meta_tc, 0x44, s24_meta_tc_bytes(M, N), stream), "output metadata prefill");
+        if (rc) return rc;
+    }
 
     int bm = cfg ? cfg->bm : 0, bn = cfg ? cfg->bn : 0;
     // Heuristic when the caller names no tile: score = (useful fraction of the persistent waves)
@@ -703,13 +781,15 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 512x224, 256x256, 256x128, 128x128)", who, bm, bn);
 }
 
-// Where the matrix covers the last 128-row tile or 128-column block only partly, the conversion
-// leaves the words outside the matrix untouched; give them a valid code before it runs (the
-// values they index are zero).  An asynchronous memset: no allocation, legal under stream capture.
-static int prefill_partial_records(void* meta_tc, int64_t M, int64_t K, cudaStream_t stream)
+// shape rules of the entry points that take the reference's metadata layout, checked before any
+// size is derived from M and K (compress_2_4.py:49-65 and :10 give the divisibility rules)
+static int check_ref_meta_shape(const char* who, int64_t M, int64_t K)
 {
-    if (M <= 0 || K <= 0 || (M % 128 == 0 && K % 128 == 0)) return S24_OK;
-    return check_cuda(cudaMemsetAsync(meta_tc, 0x44, s24_meta_tc_bytes(M, K), stream), "metadata workspace prefill");
+    if (M <= 0 || K <= 0 || M % 32 != 0 || K % 64 != 0)
+        return fail(S24_ERR_SHAPE, "%s: needs positive M %% 32 == 0 and K %% 64 == 0 (got M=%lld K=%lld)", who, (long long)M,
+                    (long long)K);
+    if (M > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return fail(S24_ERR_SHAPE, "%s: dimension too large", who);
+    return S24_OK;
 }
 
 }  // namespace s24
@@ -741,12 +821,12 @@ extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const v
                                  int64_t K, int64_t ldb, int64_t ldc, int dtype, const s24_tile_cfg* cfg,
                                  void* workspace, size_t workspace_bytes, void* stream)
 {
+    int rc = check_ref_meta_shape("spmm_ref_meta", M, K);
+    if (rc) return rc;
     if (workspace == nullptr || workspace_bytes < s24_meta_tc_bytes(M, K))
         return fail(S24_ERR_INVALID_ARG, "spmm_ref_meta: workspace of %zu bytes needed, %zu given", s24_meta_tc_bytes(M, K),
                     workspace_bytes);
     if (!aligned(workspace, 16)) return fail(S24_ERR_INVALID_ARG, "spmm_ref_meta: workspace must be 16-byte aligned");
-    int rc = prefill_partial_records(workspace, M, K, static_cast<cudaStream_t>(stream));
-    if (rc) return rc;
     rc = s24_meta_convert(meta_ref, S24_META_REF, workspace, S24_META_TC, M, K, stream);
     if (rc) return rc;
     return run_spmm(vals, workspace, B, C, M, N, K, ldb, ldc, dtype, cfg, static_cast<cudaStream_t>(stream));
@@ -762,38 +842,40 @@ extern "C" int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const v
 // device current.
 static __device__ __align__(256) unsigned char g_static_scratch[S24_STATIC_SCRATCH_BYTES];
 
-static void* static_scratch_address()
+// Device address of the built-in scratch on the current device.  Cached per device ordinal: the
+// look-up always yields the same value for a device, so concurrent first calls write the same
+// pointer (one CUDA context per device is assumed, see the header).
+static int static_scratch_address(void** out)
 {
     static void* cached[64] = {nullptr};
     int dev = 0;
-    if (check_cuda(cudaGetDevice(&dev), "cudaGetDevice") != S24_OK) return nullptr;
-    if (dev < 0 || dev >= 64) {
-        fail(S24_ERR_UNSUPPORTED, "static scratch: device ordinal %d out of range", dev);
-        return nullptr;
-    }
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return fail(S24_ERR_UNSUPPORTED, "static scratch: device ordinal %d out of range (0..63)", dev);
     if (cached[dev] == nullptr) {
         void* ptr = nullptr;
-        if (check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)") != S24_OK)
-            return nullptr;
+        rc = check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
+        if (rc) return rc;
         cached[dev] = ptr;
     }
-    return cached[dev];
+    *out = cached[dev];
+    return S24_OK;
 }
 
 extern "C" int s24_spmm_ref_meta_noalloc(const void* vals, const void* meta_ref, const void* B, void* C, int64_t M,
                                          int64_t N, int64_t K, int64_t ldb, int64_t ldc, int dtype,
                                          const s24_tile_cfg* cfg, void* stream)
 {
-    if (M <= 0 || K <= 0) return fail(S24_ERR_SHAPE, "spmm_ref_meta_noalloc: M and K must be positive");
+    int rc = check_ref_meta_shape("spmm_ref_meta_noalloc", M, K);
+    if (rc) return rc;
     const size_t need = s24_meta_tc_bytes(M, K);
     if (need > (size_t)S24_STATIC_SCRATCH_BYTES)
         return fail(S24_ERR_SHAPE,
                     "spmm_ref_meta_noalloc: metadata of a %lld x %lld matrix needs %zu bytes of scratch but the "
                     "library's built-in buffer holds %zu; use s24_spmm_ref_meta with your own workspace",
                     (long long)M, (long long)K, need, (size_t)S24_STATIC_SCRATCH_BYTES);
-    void* scratch = static_scratch_address();   // first call per device: address lookup, no allocation
-    if (scratch == nullptr) return S24_ERR_CUDA;
-    int rc = prefill_partial_records(scratch, M, K, static_cast<cudaStream_t>(stream));
+    void* scratch = nullptr;
+    rc = static_scratch_address(&scratch);   // first call per device: address lookup, no allocation
     if (rc) return rc;
     rc = s24_meta_convert(meta_ref, S24_META_REF, scratch, S24_META_TC, M, K, stream);
     if (rc) return rc;
@@ -806,6 +888,42 @@ extern "C" int s24_spmm_prune_out(const void* vals, const void* meta_tc, const v
 {
     return run_spmm(vals, meta_tc, B, nullptr, M, N, K, ldb, N, dtype, cfg, static_cast<cudaStream_t>(stream), true,
                     C_vals, C_meta_ref, C_meta_tc);
+}
+
+// ---------------------------------------------------------------- self-test of the time-out path
+//
+// A wait that nothing will ever satisfy, with a one-millisecond limit: the thread initialises a
+// barrier, waits on it, sees the wait give up and reports code 7 exactly as the GEMM's roles
+// report theirs.  Bounded by construction; leaves the context usable.
+__global__ void wait_timeout_probe_kernel(int* status, unsigned long long limit_ns)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        const uint32_t b = s24::ptx::smem_u32(&bar);
+        s24::ptx::mbar_init(b, 1);
+        s24::ptx::fence_barrier_init();
+        abort_flag = 0;
+        if (!s24::ptx::mbar_wait(b, 0, limit_ns)) s24::report_timeout(status, &abort_flag, 7);
+    }
+}
+
+extern "C" int s24_selftest_timeout(int kind, const void* vals, const void* meta_tc, const void* B, void* C, int64_t M,
+                                    int64_t N, int64_t K, int dtype, const s24_tile_cfg* cfg, void* stream)
+{
+    constexpr unsigned long long kOneMs = 1000000ull;
+    if (kind == 0) {
+        int* status = status_word_address();
+        if (status == nullptr) return fail(S24_ERR_CUDA, "selftest_timeout: cannot resolve the device status word");
+        wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, kOneMs);
+        return check_cuda(cudaGetLastError(), "selftest_timeout launch");
+    }
+    if (kind == 1) {   // the GEMM with its producer stopped after the first k-block and 1 ms waits
+        if (K < 2 * kBlockK) return fail(S24_ERR_SHAPE, "selftest_timeout: kind 1 needs K >= %d (got %lld)", 2 * kBlockK, (long long)K);
+        return run_spmm(vals, meta_tc, B, C, M, N, K, N, N, dtype, cfg, static_cast<cudaStream_t>(stream), false, nullptr,
+                        nullptr, nullptr, false, nullptr, 0, kOneMs, 1);
+    }
+    return fail(S24_ERR_INVALID_ARG, "selftest_timeout: kind must be 0 (bare wait) or 1 (starved GEMM), got %d", kind);
 }
 
 extern "C" int s24_device_status(void* stream)
@@ -821,5 +939,5 @@ extern "C" int s24_device_status(void* stream)
     if (host == 0) return S24_OK;
     cudaMemsetAsync(status, 0, sizeof(int), s);
     cudaStreamSynchronize(s);
-    return fail(S24_ERR_TIMEOUT, "a device-side wait timed out (code %d: 1 producer/empty, 2 mma/full, 3 mma/accumulator, 4 epilogue)", host);
+    return fail(S24_ERR_TIMEOUT, "a device-side wait timed out (code %d: 1 producer/empty, 2 mma/full, 3 mma/accumulator, 4 epilogue, 5 prune warp, 6 mma/pruned A, 7 self-test)", host);
 }

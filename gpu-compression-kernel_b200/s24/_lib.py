@@ -49,6 +49,7 @@ SIGNATURES = {
     "s24_peer_close": (_i32, [_vp]),
     "s24_relayout_shards": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "s24_device_status": (_i32, [_vp]),
+    "s24_selftest_timeout": (_i32, [_i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, ctypes.POINTER(TileCfg), _vp]),
 }
 
 _lib = None

@@ -58,6 +58,18 @@ class _on_device:
         return False
 
 
+# S24_CHECK_STATUS=1: after every GEMM call synchronise the stream and raise if a bounded
+# device-side wait gave up (the launch itself reports success and leaves C partly written in that
+# case).  Off by default because it serialises host and device; callers that keep it off should
+# poll s24_device_status at their own synchronisation points.
+_CHECK_STATUS = os.environ.get("S24_CHECK_STATUS", "0") not in ("", "0")
+
+
+def _after_gemm(t: torch.Tensor) -> None:
+    if _CHECK_STATUS and not torch.cuda.is_current_stream_capturing():
+        L.check(L.lib().s24_device_status(_stream(t)))
+
+
 def _require_cuda(*ts: torch.Tensor) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -82,17 +94,11 @@ def meta_tc_numel(M: int, K: int) -> int:
     return int(L.lib().s24_meta_tc_bytes(M, K)) // 4
 
 
-_TC_FILLER = 0x44444444   # a valid 2:4 code in every nibble
-
-
 def _new_meta_tc(M: int, K: int, device) -> torch.Tensor:
     """Tensor-core-layout buffer.  Records are whole (128-row tile, 128-column block) units; when the
-    matrix covers the last ones only partly, the words outside it are never written by the kernels,
-    so they are pre-set to a valid code (the values they index are zero)."""
-    n = meta_tc_numel(M, K)
-    if M % 128 == 0 and K % 128 == 0:
-        return torch.empty((n,), dtype=torch.int32, device=device)
-    return torch.full((n,), _TC_FILLER, dtype=torch.int32, device=device)
+    matrix covers the last ones only partly, the library call that fills the buffer also gives the
+    words outside the matrix a valid code (the values they index are zero)."""
+    return torch.empty((meta_tc_numel(M, K),), dtype=torch.int32, device=device)
 
 
 def prune(t: torch.Tensor, mode: str = "signed", tie: str = "reference") -> torch.Tensor:
@@ -187,8 +193,8 @@ def meta_convert(src: torch.Tensor, from_layout: str, to_layout: str, M: int, K:
 def _tile_cfg(manual_config: Optional[dict]):
     if not manual_config:
         return None
-    cfg = L.TileCfg(int(manual_config.get("BM", 0)), int(manual_config.get("BN", 0)),
-                    int(manual_config.get("buffers", 0)), 0)
+    # the ring depth ("buffers" in the reference's configs) is fixed per tile shape here
+    cfg = L.TileCfg(int(manual_config.get("BM", 0)), int(manual_config.get("BN", 0)), 0, 0)
     return ctypes.byref(cfg)
 
 
@@ -285,6 +291,7 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
             _check_meta_tc(meta, M, K)
             L.check(L.lib().s24_spmm_bt(_p(v), _p(meta), _p(B), _p(c), M, N, K, B.stride(1), c.stride(0),
                                         _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
+            _after_gemm(vals)
         return c
     b = _row_major(B)
     if out is not None:
@@ -317,6 +324,7 @@ def spmm(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta_layout: s
                                               workspace.numel() * 4, _stream(vals)))
         else:
             raise ValueError(f"unknown metadata layout {meta_layout!r}")
+        _after_gemm(vals)
     return c
 
 
@@ -346,6 +354,7 @@ def spmm_prune_out(vals: torch.Tensor, meta: torch.Tensor, B: torch.Tensor, meta
     with _on_device(vals):
         L.check(L.lib().s24_spmm_prune_out(_p(v), _p(meta_tc), _p(b), _p(cv), _p(ce), _p(ct), M, N, K,
                                            b.stride(0), _DT[vals.dtype], _tile_cfg(manual_config), _stream(vals)))
+        _after_gemm(vals)
     return cv, ce, ct
 
 
@@ -376,6 +385,7 @@ def spmm_prune_in(A: torch.Tensor, B: torch.Tensor, mode: str = "signed", tie: s
     with _on_device(A):
         L.check(L.lib().s24_spmm_prune_in(_p(a), a.stride(0), _p(b), _p(c), M, N, K, b.stride(0), c.stride(0),
                                           _DT[A.dtype], _MODE[mode], _TIE[tie], _stream(A)))
+        _after_gemm(A)
     return c
 
 

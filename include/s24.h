@@ -9,6 +9,16 @@
  * set-up and debug helpers and say so: s24_peer_alloc / s24_peer_free / s24_peer_open /
  * s24_peer_close (multi-GPU buffers) and s24_device_status (reads a status word back).
  *
+ * Per-device state.  The library caches three things per device ordinal, each written once
+ * with the same value whichever thread gets there first (so concurrent first calls are
+ * benign, but the caches are not locked): the SM count, the large-shared-memory opt-in of
+ * each GEMM variant, and the device addresses of two objects inside the library image (the
+ * status word and the built-in scratch buffer, looked up with cudaGetSymbolAddress).  They
+ * assume one CUDA context per device for the life of the process (the primary context that
+ * the runtime API uses); after cudaDeviceReset the library must be reloaded.  The first GEMM
+ * call on a device performs these look-ups: make it, with the device current, before any
+ * stream capture.  Up to 64 devices.
+ *
  * The entry points replace, one for one, the GPU work behind these functions of the
  * reference project (paths relative to its root):
  *
@@ -37,10 +47,11 @@
  *                     This is the image tcgen05.cp (128x128b) moves into tensor memory for
  *                     four consecutive tcgen05.mma.sp instructions of K = 32.
  *                     There are ceil(M/128) x ceil(K/128) whole records; where M or K is not a
- *                     multiple of 128 the words of rows >= M and of columns >= K are not
- *                     written by the library and must hold valid codes when a GEMM reads them
- *                     (the values they index read as zero): fill the buffer with 0x44 bytes
- *                     before the first use, as the Python front end does.
+ *                     multiple of 128 the words of rows >= M and of columns >= K hold a filler
+ *                     code (0x44 bytes; the values they index read as zero).  Every entry
+ *                     point that writes this layout sets the filler itself, with an
+ *                     asynchronous memset on the caller's stream before its kernel; a caller
+ *                     that builds such a buffer on its own must do the same.
  */
 #ifndef S24_H_
 #define S24_H_
@@ -77,7 +88,10 @@ extern "C" {
 #define S24_MODE_MAGNITUDE 1       /* |value| */
 
 /* which element survives when the 2nd and 3rd largest keys are equal */
-#define S24_TIE_REFERENCE 0        /* exactly what the reference's CPU torch.topk does */
+#define S24_TIE_REFERENCE 0        /* exactly what prune_2_4 does on CPU tensors: the tie order of
+                                      torch.topk(k=2, largest=False) in torch 2.11.0 (CPU), measured
+                                      over all 75 weak orderings of four keys; torch.topk on CUDA
+                                      tensors, or another torch release, may order ties differently */
 #define S24_TIE_LOWER 1            /* lower index survives (kernels/10.1_prune_acc.py:100-105) */
 #define S24_TIE_HIGHER 2           /* higher index survives (kernels/11.1_2_kernel_baseline.py:95-100) */
 
@@ -91,7 +105,8 @@ extern "C" {
 typedef struct s24_tile_cfg {
     int bm;        /* rows per tile: 128 (one CTA), 256 (CTA pair) or 512 (CTA pair, two row sub-tiles), 0 = auto */
     int bn;        /* columns per tile: 128 or 256; 224 with bm = 512; 0 = auto */
-    int stages;    /* depth of the shared-memory ring, 0 = auto */
+    int stages;    /* reserved, ignored: every tile shape has one ring depth (512x224: 3, 256x256: 4,
+                      256x128: 6, 128x128: 4 stages of K = 128) that fills the 227 KB of shared memory */
     int reserved;
 } s24_tile_cfg;
 
@@ -189,8 +204,10 @@ S24_API int s24_spmm_ref_meta(const void* vals, const void* meta_ref, const void
  * part of the library image on the device (every GPU that loads libs24 holds these bytes
  * until the process exits).  No cudaMalloc, cudaFree or allocating library routine is
  * called.  Limits and rules:
- *   - M * K / 8 must not exceed S24_STATIC_SCRATCH_BYTES (M * K <= 2^26, e.g. 8192 x 8192);
- *     larger problems are rejected with S24_ERR_SHAPE and a message naming both sizes;
+ *   - s24_meta_tc_bytes(M, K) = ceil(M/128) * ceil(K/128) * 2048 must not exceed
+ *     S24_STATIC_SCRATCH_BYTES (8192 x 8192 fits exactly; for multiples of 128 the rule reads
+ *     M * K <= 2^26, other shapes count whole 128 x 128 records); larger problems are
+ *     rejected with S24_ERR_SHAPE and a message naming both sizes;
  *   - the first call on each device looks up the buffer's device address
  *     (cudaGetSymbolAddress) and caches it; make that first call, with the device current,
  *     before any stream capture you may use;
@@ -279,12 +296,29 @@ S24_API int s24_relayout_shards(const void* stage, void* out, int64_t rows, int6
 
 /*
  * Debug / test aid (no counterpart in the reference): every device-side wait in the GEMM
- * kernels is bounded; if one gives up the kernel records a code and returns.  This call
+ * kernels is bounded (2 s); if one gives up the kernel records a code, frees its tensor memory
+ * and returns, and the launch itself still reports S24_OK with C partly written.  This call
  * synchronises `stream`, returns S24_OK if no kernel on the current device has reported a
  * failure since the last call, else S24_ERR_TIMEOUT (code in s24_last_error()), and clears
- * the record.
+ * the record.  A caller that must not consume a partly written result polls it at its next
+ * synchronisation point (the Python front end does so after every GEMM when S24_CHECK_STATUS=1).
  */
 S24_API int s24_device_status(void* stream);
+
+/*
+ * Self-test of that time-out path (no counterpart in the reference).  Nothing here can hang:
+ * every wait involved gives up after one millisecond.
+ *   kind 0: one thread waits on a barrier that nothing will ever complete, sees the wait run
+ *           out and records code 7.  The operand arguments are ignored (pass NULL / 0).
+ *   kind 1: the GEMM s24_spmm would run for these operands (ldb = ldc = N), except that its
+ *           producer stops loading after the first k-block, so the MMA and epilogue roles run
+ *           out of data, take their time-out branches, the kernel frees its tensor memory and
+ *           returns.  K must span at least two k-blocks of 128.  C is left partly written.
+ * Either way the launch returns S24_OK and s24_device_status() then reports S24_ERR_TIMEOUT
+ * once; the context stays usable.
+ */
+S24_API int s24_selftest_timeout(int kind, const void* vals, const void* meta_tc, const void* B, void* C,
+                         int64_t M, int64_t N, int64_t K, int dtype, const s24_tile_cfg* cfg, void* stream);
 
 #ifdef __cplusplus
 }

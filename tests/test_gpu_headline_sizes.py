@@ -1,0 +1,152 @@
+"""GPU parity at the sizes the benchmark numbers are quoted on.
+
+The reference checks itself at full size (compression/gluon_ws_sparse.py:643-660 at 49152^2,
+compression/kernels/11.1_2_kernel_baseline.py:376-392 at 49152 x 8192 x 49152,
+compression/kernels/10.1_prune_acc.py:715-781) against `A_pruned @ B` in torch.  A CPU oracle cannot
+multiply matrices of that size in seconds, so the products are compared on sampled 128-row panels:
+the sparse operand is pruned (and, where the library is handed compressed input, compressed) by
+the CPU oracle, the panel's rows of the pruned matrix are multiplied by the whole B in fp32 on
+the GPU (TF32 off) and the kernel's rows must agree within rtol = atol = 1e-2.  Panels are
+placed where tile-count-dependent mistakes would show: the first tile, the last row tile of a
+raster group of eight, the first tile of the next group, the last tile; every panel spans all
+columns, so the ragged last column tile of the 512 x 224 shape is included.
+"""
+import numpy as np
+import pytest
+import torch
+
+from util import ODT, bits, from_bits, load_dropin, oracle, randn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+RTOL = ATOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def mods():
+    import s24
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return {"s24": s24, "ws": load_dropin("gluon_ws_sparse.py"), "two": load_dropin("kernels/11.1_2_kernel_baseline.py"),
+            "v101": load_dropin("kernels/10.1_prune_acc.py")}
+
+
+def _status_ok():
+    from s24 import _lib
+    assert _lib.lib().s24_device_status(None) == 0, _lib.last_error()
+
+
+def _panel_reference(ap_bits, r0, B_dev, dtype):
+    """fp32 product of rows r0..r0+127 of the oracle-pruned matrix with B (on the GPU, TF32 off)"""
+    return from_bits(ap_bits[r0:r0 + 128], dtype, DEV).float() @ B_dev.float()
+
+
+def _check_panel(C_rows, ref32):
+    torch.testing.assert_close(C_rows.float(), ref32.to(C_rows.dtype).float(), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(C_rows.float(), ref32, rtol=RTOL, atol=ATOL + 4e-3 * float(ref32.abs().max()))
+
+
+@pytest.fixture(scope="module")
+def cfg_8192():
+    """A 8192 x 8192 fp16 N(0, 1) pruned and compressed by the CPU oracle, B 8192 x 8192 N(0, 1)"""
+    M = K = N = 8192
+    A = randn((M, K), torch.float16, 4000)
+    B = randn((K, N), torch.float16, 4001).to(DEV)
+    ap = oracle.prune(bits(A), oracle.FP16)
+    vals, ml, e = oracle.compress(ap, oracle.FP16)
+    return {"ap": ap, "vals": from_bits(vals, torch.float16, DEV), "E": torch.from_numpy(e).to(DEV).view(M // 16, K), "B": B}
+
+
+PANELS_8192 = (0, 3584, 3968, 4096, 8064)   # 3968: last 128 rows of raster group 0 (row tiles of 512)
+
+
+@pytest.mark.parametrize("cfg", [None, {"BM": 256, "BN": 256}])
+def test_sparse_gemm_8192_cubed_normal_data(mods, cfg_8192, cfg):
+    """the headline workload itself: run_sparse_ws_matmul(A_vals, E, B) at M = K = N = 8192 on N(0, 1) data,
+    default tile (512 x 224: 16 x 37 tiles, the 37th column tile ragged) and 256 x 256"""
+    d = cfg_8192
+    C = mods["ws"].run_sparse_ws_matmul(d["vals"], d["E"], d["B"], tune=False, manual_config=cfg)
+    _status_ok()
+    assert C.shape == (8192, 8192) and C.dtype == torch.float16
+    for r0 in PANELS_8192:
+        _check_panel(C[r0:r0 + 128], _panel_reference(d["ap"], r0, d["B"], torch.float16))
+
+
+def _codes_to_mask(meta_logical: np.ndarray) -> np.ndarray:
+    w = meta_logical.view(np.uint16).astype(np.uint32)
+    codes = np.stack([(w >> (4 * j)) & 0xF for j in range(4)], axis=-1).reshape(w.shape[0], -1)
+    return ((1 << (codes & 3)) | (1 << (codes >> 2))).astype(np.uint8)
+
+
+@pytest.mark.parametrize("cfg", [None, {"BM": 256, "BN": 256}])
+def test_fused_output_prune_8192_cubed(mods, cfg_8192, cfg):
+    """cfg 4: the pruning epilogue at 8192^3.  On every sampled panel the keep mask must equal the
+    oracle's prune of the fp32 product (signed keys, lower index wins) except in groups whose 2nd and
+    3rd largest values are closer than the GEMM tolerance; stored values are the masked elements."""
+    d = cfg_8192
+    M = N = 8192
+    cv, ce = mods["v101"].run_sparse_ws_matmul(d["vals"], d["E"], d["B"], tune=False, manual_config=cfg)
+    _status_ok()
+    assert cv.shape == (M, N // 2) and ce.shape == (M // 16, N)
+    off = oracle.meta_offsets(128, N // 16)     # the reference layout is made of independent 16-row groups
+    for r0 in PANELS_8192:
+        c32 = _panel_reference(d["ap"], r0, d["B"], torch.float16).cpu().numpy()
+        _, want_mask = oracle.prune_f32(c32, oracle.MODE_SIGNED, oracle.TIE_LOWER, return_mask=True)
+        got_ml = ce[r0 // 16:(r0 + 128) // 16].cpu().numpy().reshape(-1)[off].reshape(128, N // 16)
+        got_mask = _codes_to_mask(got_ml)
+        assert np.isin(got_mask, [0b0011, 0b0101, 0b0110, 0b1001, 0b1010, 0b1100]).all()
+        groups = c32.reshape(128, N // 4, 4)
+        srt = np.sort(groups, axis=-1)
+        second, third = srt[..., 2], srt[..., 1]
+        near_tie = np.abs(second - third) <= ATOL + RTOL * np.abs(second)
+        differ = got_mask != want_mask
+        assert not (differ & ~near_tie).any(), f"panel {r0}: {int((differ & ~near_tie).sum())} masks differ away from near-ties"
+        got_v = cv[r0:r0 + 128].float().cpu().numpy().reshape(128, N // 4, 2)
+        bitsel = (got_mask[..., None] >> np.arange(4)) & 1
+        idx = np.argsort(-bitsel, axis=-1, kind="stable")[..., :2]
+        idx.sort(axis=-1)
+        picked = np.take_along_axis(groups, idx, axis=-1)
+        np.testing.assert_allclose(got_v, picked, rtol=RTOL, atol=ATOL + 2e-3 * float(np.abs(c32).max()))
+
+
+def test_mlp_shard_shape_bf16_row_major_and_transposed(mods):
+    """cfg 5, one GPU's share: W 28672 x 8192 bf16 ~ N(0, 0.02) (2:4) times an 8192-column shard of the
+    activations, given row-major (K, N) and as the transposed view of (tokens, hidden) storage"""
+    s24 = mods["s24"]
+    M, K, N = 28672, 8192, 8192
+    W = randn((M, K), torch.bfloat16, 5000, scale=0.02)
+    X = randn((K, N), torch.bfloat16, 5001).to(DEV)
+    ap = oracle.prune(bits(W), oracle.BF16)
+    vals, ml, e = oracle.compress(ap, oracle.BF16)
+    v = from_bits(vals, torch.bfloat16, DEV)
+    E = torch.from_numpy(e).to(DEV).view(M // 16, K)
+    del W, vals, ml, e
+    C = mods["ws"].run_sparse_ws_matmul(v, E, X, tune=False)
+    Xt = X.t().contiguous()                       # (N, K) row-major: activations stored (tokens, hidden)
+    C_t = s24.spmm(v, E, Xt.t(), meta_layout="ref")
+    _status_ok()
+    assert torch.equal(C, C_t)
+    for r0 in (0, 3968, 4096, 14336, 28544):      # 56 row tiles of 512 = 7 raster groups
+        ref32 = _panel_reference(ap, r0, X, torch.bfloat16)
+        torch.testing.assert_close(C[r0:r0 + 128].float(), ref32, rtol=RTOL, atol=ATOL)
+
+
+def test_two_kernel_path_at_the_reference_self_check_shape(mods):
+    """(M, N, K) = (49152, 8192, 49152), the shape the reference's two-kernel script checks itself on
+    (11.1_2_kernel_baseline.py:376-392): dense A -> prune+compress kernel -> sparse GEMM.  A is 4.8 GB,
+    so only the sampled panels' rows go through the CPU oracle (strict compare, the higher index
+    survives a tie, as in the reference's kernel :95-100)."""
+    M, N, K = 49152, 8192, 49152
+    g = torch.Generator(device=DEV).manual_seed(49152)
+    A = torch.randn(M, K, generator=g, device=DEV, dtype=torch.float16)
+    B = torch.randn(K, N, generator=g, device=DEV, dtype=torch.float16)
+    D = mods["two"].run_2_kernel_ws_matmul(A, B, tune=False)
+    _status_ok()
+    assert D.shape == (M, N)
+    for r0 in (0, 43776, 49024):
+        ap = oracle.prune(bits(A[r0:r0 + 128]), oracle.FP16, oracle.MODE_SIGNED, oracle.TIE_HIGHER)
+        ref32 = from_bits(ap, torch.float16, DEV).float() @ B.float()
+        _check_panel(D[r0:r0 + 128], ref32)
+        # the reference's own criterion (fp16 torch product, rtol 1e-3, atol 1e-1)
+        torch.testing.assert_close(D[r0:r0 + 128], (from_bits(ap, torch.float16, DEV) @ B), rtol=1e-3, atol=1e-1)
+    del A, B, D
+    torch.cuda.empty_cache()

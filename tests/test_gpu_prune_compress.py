@@ -102,6 +102,24 @@ def test_prune_accepts_any_leading_shape_and_odd_group_counts(mods):
     assert np.array_equal(bits(got), oracle.prune(bits(base[:, 4:]), oracle.FP16))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_prune_in_place_through_the_c_abi(mods, dtype):
+    """s24_prune documents that `out` may equal `A`: prune a buffer onto itself, 16-byte aligned and
+    (a view 4 elements in) 8-byte aligned only, large enough for the grid-stride loop to wrap"""
+    import ctypes
+    from s24 import _lib
+    L = _lib.lib()
+    for offset, n in ((0, 1 << 22), (4, (1 << 22) - 8), (0, 2048)):
+        buf = tie_heavy((1, (1 << 22) + 8), dtype, 31 + offset).to(DEV) if n < 4096 else randn((1, (1 << 22) + 8), dtype, 33 + offset).to(DEV)
+        view = buf[0, offset:offset + n]
+        want = oracle.prune(bits(view).reshape(-1, 4), ODT[dtype]).reshape(-1)
+        ptr = ctypes.c_void_p(view.data_ptr())
+        _lib.check(L.s24_prune(ptr, ptr, n, _lib.FP16 if dtype == torch.float16 else _lib.BF16, _lib.MODE_SIGNED,
+                               _lib.TIE_REFERENCE, None))
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(view), want)
+
+
 def test_input_is_not_modified_and_strided_rows_work(mods):
     big = randn((64, 256), torch.float16, 3).to(DEV)
     A = big[:, :128]                      # row stride 256, not contiguous
