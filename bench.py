@@ -363,22 +363,25 @@ def leg_cfg5(args, rank, world, dev, stream, barrier):
     ms_shard = timed(lambda: op(X), 10)
     ms_rep = timed(lambda: op(X, n_total=N, replicated=True, panels=8), steps)
     ms_fused = timed(lambda: op(X, n_total=N, replicated="fused"), steps)
+    ms_copy = timed(lambda: op(X, n_total=N, replicated="copy", panels=4), steps)
     recv = M * N * 2 * (world - 1) // world          # bytes every GPU receives (all-gather) / stores to peers (fused)
     # ---- untimed: every shard of both replicated results against the product recomputed on this GPU
     C_gath = op(X, n_total=N, replicated=True, panels=8)
-    C_fused = op(X, n_total=N, replicated="fused")
+    C_fused = op(X, n_total=N, replicated="fused").clone()      # "fused" and "copy" return the same reused buffer
+    C_copy = op(X, n_total=N, replicated="copy", panels=4)
     torch.cuda.synchronize(dev)
-    ok_g = ok_f = True
+    ok_g = ok_f = ok_c = True
     for r in range(world):
         Xr = X if r == rank else shard_of(r)
         want = s24.spmm(vals, tc, Xr)                                                   # library's default tile
         want_f = s24.spmm(vals, tc, Xr, manual_config={"BM": 256, "BN": 256})           # the scatter kernel's tile
         ok_g = ok_g and torch.equal(C_gath[:, r * nl:(r + 1) * nl], want)
         ok_f = ok_f and torch.equal(C_fused[:, r * nl:(r + 1) * nl], want_f)
+        ok_c = ok_c and torch.equal(C_copy[:, r * nl:(r + 1) * nl], want)
         del want, want_f
-    flags = torch.tensor([int(ok_g), int(ok_f)], device=dev, dtype=torch.int32)
+    flags = torch.tensor([int(ok_g), int(ok_f), int(ok_c)], device=dev, dtype=torch.int32)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
-    del C_gath, C_fused
+    del C_gath, C_fused, C_copy
     op.close()
     return {
         "workload": f"W24 {M}x{K} bf16 (2:4, ~N(0, 0.02)) . X {K}x{N} bf16, output columns split over {world} GPUs",
@@ -392,6 +395,12 @@ def leg_cfg5(args, rank, world, dev, stream, barrier):
                              "gbs_per_gpu": recv / (ms_fused * 1e-3) / 1e9, "frac_of_peer_copy_770gbs": recv / (ms_fused * 1e-3) / 1e9 / 770.0,
                              "how": "one kernel: the GEMM epilogue stores each tile into every rank's peer-mapped copy of C (bulk stores over NVLink)",
                              "equals_recomputed_shards": bool(flags[1].item())},
+        "replicated_copy": {"ms": ms_copy, "tflops": flops / ms_copy / 1e9, "pushed_to_peers_bytes_per_gpu": recv,
+                            "gbs_per_gpu": recv / (ms_copy * 1e-3) / 1e9, "frac_of_peer_copy_770gbs": recv / (ms_copy * 1e-3) / 1e9 / 770.0,
+                            "how": "GEMM in 4 row panels writing in place into this rank's copy of C; each finished panel is pushed to "
+                                   "the peers' copies by the copy engines (pitched peer copies, one stream per destination) while "
+                                   "the next panel multiplies; no SM is spent on the exchange",
+                            "equals_recomputed_shards": bool(flags[2].item())},
     }
 
 
@@ -640,6 +649,24 @@ def run_ours(args, rank, world, local):
         extra["fused_out"] = {"workload": "s24_spmm_prune_out at M=K=N=8192 fp16 (C stored as values + reference-layout metadata)",
                               "tile": best, **fo[best], "tiles": fo, "reference_h100_ratio": 0.98}
         check_status("the two-kernel / fused-output legs")
+        # same-box comparison lines on the same operands: cuBLAS dense on the pruned A (stands in for the
+        # reference's dense warp-specialised kernel) and the vendor's 2:4 path (cuSPARSELt behind torch's
+        # semi-structured tensor, the counterpart of the reference's torchao line, dev/8.11_benchmark_2_kernel.py:95-148)
+        A_pruned = s24.prune(A)
+        ms_dense = med3(lambda: torch.matmul(A_pruned, B, out=C))
+        extra["dense_cublas"] = {"ms": ms_dense, "tflops": flops_gemm / ms_dense / 1e9,
+                                 "workload": "torch.matmul(A_pruned, B) fp16 at 8192^3 (cuBLAS)"}
+        try:
+            from torch.sparse import to_sparse_semi_structured
+            A_sp = to_sparse_semi_structured(A_pruned)
+            ms_v = med3(lambda: torch.mm(A_sp, B))
+            extra["vendor_sparse"] = {"ms": ms_v, "tflops": flops_gemm / ms_v / 1e9,
+                                      "workload": "torch.mm(to_sparse_semi_structured(A_pruned), B) fp16 at 8192^3 "
+                                                  "(cuSPARSELt / CUTLASS behind torch, operand compressed beforehand)"}
+            del A_sp
+        except Exception as exc:      # library missing or shape unsupported on this box
+            extra["vendor_sparse"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        del A_pruned
         # cfg 1: the reference's CPU-runnable case; operands + output (68 MB) fit in L2, so warm and cold differ
         g1 = torch.Generator(device=dev).manual_seed(1234)
         A1 = torch.randn(2048, 2048, generator=g1, device=dev, dtype=torch.float32).to(torch.float16)

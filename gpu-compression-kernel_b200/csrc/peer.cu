@@ -52,3 +52,20 @@ extern "C" int s24_peer_close(void* ptr)
     if (ptr == nullptr) return S24_OK;
     return check_cuda(cudaIpcCloseMemHandle(ptr), "peer_close: cudaIpcCloseMemHandle");
 }
+
+// A block of rows, `width_bytes` wide, from one pitched buffer to another: the transfer of a
+// column shard of a row-major matrix into a peer's copy of that matrix.  Runs on the copy
+// engines (cudaMemcpy2DAsync), so it needs no SM and overlaps a persistent GEMM; dst may be a
+// peer mapping obtained from s24_peer_open.
+extern "C" int s24_peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                                size_t rows, void* stream)
+{
+    if (dst == nullptr || src == nullptr) return fail(S24_ERR_INVALID_ARG, "peer_copy_2d: null pointer");
+    if (width_bytes == 0 || rows == 0) return S24_OK;
+    if (dst_pitch < width_bytes || src_pitch < width_bytes)
+        return fail(S24_ERR_SHAPE, "peer_copy_2d: pitches (%zu, %zu) must be at least the width (%zu bytes)", dst_pitch, src_pitch,
+                    width_bytes);
+    return check_cuda(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                                        static_cast<cudaStream_t>(stream)),
+                      "peer_copy_2d: cudaMemcpy2DAsync");
+}

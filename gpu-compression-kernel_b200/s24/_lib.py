@@ -47,6 +47,7 @@ SIGNATURES = {
     "s24_peer_export": (_i32, [_vp, _vp]),
     "s24_peer_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
     "s24_peer_close": (_i32, [_vp]),
+    "s24_peer_copy_2d": (_i32, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
     "s24_relayout_shards": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "s24_device_status": (_i32, [_vp]),
     "s24_selftest_timeout": (_i32, [_i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, ctypes.POINTER(TileCfg), _vp]),

@@ -7,7 +7,10 @@ is used only when the caller asks for a replicated result; then C is all-gathere
 panels so that the gather of one panel overlaps the GEMM of the next.  With replicated="fused"
 there is no separate collective at all: every rank's copy of C lives in a buffer that the other
 ranks have mapped (`PeerBuffer`), and each rank's GEMM stores its column shard into all copies
-from its epilogue, so the shard crosses NVLink tile by tile while the GEMM runs.
+from its epilogue, so the shard crosses NVLink tile by tile while the GEMM runs.  With
+replicated="copy" the GEMM runs in row panels on its best tile, writing straight into its place in
+this rank's copy of C, and each finished panel is pushed to the other ranks' copies by the copy
+engines (pitched peer copies on side streams) while the SMs multiply the next panel.
 
 The reference project is single-GPU; this module has no counterpart there.
 """
@@ -75,6 +78,10 @@ class _CudaPeerBackend:
     def close(self, ptr: int) -> None:
         from . import ops
         ops.peer_close(ptr)
+
+    def copy_2d(self, dst: int, dst_pitch: int, src: int, src_pitch: int, width_bytes: int, rows: int, stream) -> None:
+        from . import ops
+        ops.peer_copy_2d(dst, dst_pitch, src, src_pitch, width_bytes, rows, stream)
 
     def as_tensor(self, ptr: int, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
         class _Raw:   # zero-copy view of the allocation through the CUDA array interface
@@ -166,6 +173,7 @@ class NShardedSpmm:
         self.scatter_fn = scatter_fn or _default_scatter   # scatter_fn(vals, meta_tc, B_shard, dst_ptrs, ldc)
         self.peer_backend = peer_backend
         self._peer: Optional[PeerBuffer] = None
+        self._copy_streams: List = []
         self._fence_flag: Optional[torch.Tensor] = None
 
     def local_columns(self, n_total: int) -> Tuple[int, int]:
@@ -175,6 +183,8 @@ class NShardedSpmm:
                  panels: int = 4) -> torch.Tensor:
         """B_shard: this rank's (K, N_local) columns of B.  Returns the local (M, N_local)
         shard of C, or with replicated=True the full (M, n_total) C on every rank (all-gather).
+        replicated="copy" gives the same result with the shards pushed by the copy engines, panel by
+        panel, while the GEMM of the next panel runs (result buffer owned and reused like "fused").
         replicated="fused" gives the same result without a collective on the data path: the GEMM
         itself stores each shard into every rank's copy of C.  That copy is a buffer owned by this
         object and is returned again (overwritten) by the next fused call of the same shape."""
@@ -190,6 +200,8 @@ class NShardedSpmm:
                                f"(N_local={n_local}, world={self.world}, N={n_total})")
         if replicated == "fused":
             return self._fused(B_shard, n_total)
+        if replicated == "copy":
+            return self._copied(B_shard, n_total, panels)
         return self._gathered(B_shard, n_total, panels)
 
     def _fence(self, device: torch.device) -> None:
@@ -216,6 +228,50 @@ class NShardedSpmm:
         self.scatter_fn(self.vals, self.meta_tc, B_shard, dsts, n_total)
         self._fence(dev)          # every rank's shard has landed in every copy
         return buf.tensor
+
+    def _copied(self, B_shard: torch.Tensor, n_total: int, panels: int) -> torch.Tensor:
+        M, G, nl = self.M, self.world, B_shard.shape[1]
+        dev = B_shard.device
+        if self._peer is not None and (self._peer.rows, self._peer.cols) != (M, n_total):
+            self._peer.close()
+            self._peer = None
+        if self._peer is None:
+            self._peer = PeerBuffer(M, n_total, self.vals.dtype, dev, group=self.group, backend=self.peer_backend)
+        buf = self._peer
+        cuda = dev.type == "cuda"
+        if cuda and not self._copy_streams:
+            self._copy_streams = [torch.cuda.Stream(device=dev) for _ in range(G - 1)]   # one per destination
+        compute = torch.cuda.current_stream(dev) if cuda else None
+        self._fence(dev)          # every rank is done reading the previous result
+        col0 = self.rank * nl
+        pitch = n_total * 2
+        mine = buf.tensor[:, col0:col0 + nl]               # this rank's columns of its own copy
+        for (r0, r1) in row_panels(M, panels):
+            # the panel's product lands in place: row stride n_total, no staging buffer
+            self.spmm_fn(self.vals[r0:r1], self._meta_rows(r0, r1), B_shard, out=mine[r0:r1])
+            off = (r0 * n_total + col0) * 2
+            ev = None
+            if cuda:
+                ev = torch.cuda.Event()
+                ev.record(compute)
+            # round the ring starting after this rank, so that at any moment the ranks push to different peers
+            for i in range(1, G):
+                g = (self.rank + i) % G
+                st = self._copy_streams[i - 1] if cuda else None
+                if cuda:
+                    st.wait_event(ev)
+                self.backend_copy(buf, buf.ptrs[g] + off, pitch, buf.ptrs[self.rank] + off, pitch, nl * 2, r1 - r0, st)
+        if cuda:
+            for st in self._copy_streams:
+                done = torch.cuda.Event()
+                done.record(st)
+                compute.wait_event(done)
+        self._fence(dev)          # every rank's panels have landed in every copy
+        return buf.tensor
+
+    @staticmethod
+    def backend_copy(buf: "PeerBuffer", dst, dst_pitch, src, src_pitch, width_bytes, rows, stream) -> None:
+        buf.backend.copy_2d(dst, dst_pitch, src, src_pitch, width_bytes, rows, stream)
 
     def close(self) -> None:
         """release the peer-mapped result buffer (collective)"""

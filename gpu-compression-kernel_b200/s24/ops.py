@@ -439,6 +439,13 @@ def peer_close(ptr: int) -> None:
     L.check(L.lib().s24_peer_close(ctypes.c_void_p(ptr)))
 
 
+def peer_copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width_bytes: int, rows: int,
+                 stream: torch.cuda.Stream) -> None:
+    """enqueue a pitched block copy (copy engines) on `stream`; dst may be a peer mapping"""
+    L.check(L.lib().s24_peer_copy_2d(ctypes.c_void_p(dst_ptr), int(dst_pitch), ctypes.c_void_p(src_ptr), int(src_pitch),
+                                     int(width_bytes), int(rows), ctypes.c_void_p(stream.cuda_stream)))
+
+
 def relayout_shards(stage: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """stage (G, rows, nl) shard-major -> out (rows, G * nl) row-major (see s24_relayout_shards)."""
     _require_cuda(stage, out)

@@ -285,6 +285,16 @@ S24_API int s24_peer_open(const void* handle, void** ptr);
 S24_API int s24_peer_close(void* ptr);
 
 /*
+ * Copy `rows` rows of `width_bytes` bytes from src (row pitch src_pitch bytes) to dst (row pitch
+ * dst_pitch bytes) on `stream` with the copy engines (no counterpart in the reference).  dst may
+ * be a mapping from s24_peer_open: this is how a rank pushes its column shard of C into the other
+ * ranks' copies of C while its SMs keep multiplying the next row panel.  Enqueues only; the
+ * caller orders the ranks afterwards as for s24_spmm_scatter.
+ */
+S24_API int s24_peer_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t rows, void* stream);
+
+/*
  * Multi-GPU helper (the reference is single-GPU; no counterpart there).  When C is computed in
  * column shards, one per rank, an all-gather delivers them shard-major: stage is
  * (shards, rows, shard_cols) contiguous, 16-bit elements.  This writes the row-major matrix

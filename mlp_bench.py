@@ -4,7 +4,7 @@ the 65536 columns are split over 1 / 2 / 4 / 8 GPUs), without a replicated resul
 by an NCCL all-gather, and with one made by the GEMM storing each shard into all ranks' copies.  Launch one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
-        gpu-compression-kernel_b200/mlp_bench.py [--steps 10]
+        mlp_bench.py [--steps 10]
 
 Rank 0 prints one JSON line: aggregate dense-equivalent TFLOP/s (max-over-ranks device time)
 for the sharded result and for the two replicated ones.
@@ -12,6 +12,7 @@ for the sharded result and for the two replicated ones.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import sys
@@ -20,7 +21,7 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 
-sys.path.insert(0, str(Path(__file__).resolve().parent))
+sys.path.insert(0, str(Path(__file__).resolve().parent / "gpu-compression-kernel_b200"))
 import s24  # noqa: E402
 from s24.multi import NShardedSpmm  # noqa: E402
 
@@ -36,7 +37,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     g = torch.Generator(device=dev).manual_seed(5000)                    # same W on every rank
     W = (0.02 * torch.randn(M, K, generator=g, device=dev, dtype=torch.float32)).to(torch.bfloat16)
     vals, _, tc = s24.prune_compress(W, want_ref=False, want_tc=True)    # compressed redundantly, no broadcast

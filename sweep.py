@@ -3,8 +3,8 @@
 compression/dev/8.11.1_benchmark_pruning.py for prune+compress,
 compression/dev/8.10_benchmark_post_compression.py for the fused-output lines).
 
-    python gpu-compression-kernel_b200/sweep.py [--n 8192] [--dtype fp16|bf16] [--quick] [--out results.jsonl]
-    python gpu-compression-kernel_b200/sweep.py --table results.jsonl        # markdown table, no GPU needed
+    python sweep.py [--n 8192] [--dtype fp16|bf16] [--quick] [--out results.jsonl]
+    python sweep.py --table results.jsonl        # markdown table, no GPU needed
 
 For every (M, K) of the reference's 13 x 13 grid (N fixed) it appends one JSON line with, in
 the reference's units (dense-equivalent TFLOP/s = 2 M N K / t, GB/s = 3.125 M K / t):
@@ -33,7 +33,7 @@ from pathlib import Path
 import torch
 
 HERE = Path(__file__).resolve().parent
-sys.path.insert(0, str(HERE))
+sys.path.insert(0, str(HERE / "gpu-compression-kernel_b200"))
 import s24  # noqa: E402
 
 GRID = [768, 1024, 1536, 2048, 3072, 4096, 6144, 8192, 12288, 16384, 24576, 32768, 49152]

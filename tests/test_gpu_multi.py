@@ -21,7 +21,8 @@ from s24.multi import NShardedSpmm
 rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
 torch.cuda.set_device(local)
 dev = torch.device("cuda", local)
-dist.init_process_group("nccl", device_id=dev)
+import datetime
+dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
 torch.backends.cuda.matmul.allow_tf32 = False
 M, K, N = 1024, 1024, 512 * world
 g = torch.Generator().manual_seed(99)
@@ -47,6 +48,14 @@ for it in range(3):
     C_fused = op(Bi[:, n0:n1].contiguous(), n_total=N, replicated="fused")
     torch.cuda.synchronize()
     assert torch.equal(C_fused, wi), f"fused replicated result differs (iteration {{it}})"
+# the same replicated result with the shards pushed by the copy engines, row panel by row panel, while
+# the next panel multiplies; the GEMM writes in place with its default tiles
+for it in range(3):
+    Bi = B if it == 0 else torch.roll(B, it, dims=0)
+    wi = single if it == 0 else s24.spmm(vals, tc, Bi)
+    C_copy = op(Bi[:, n0:n1].contiguous(), n_total=N, replicated="copy", panels=4)
+    torch.cuda.synchronize()
+    assert torch.equal(C_copy, wi), f"copy-engine replicated result differs (iteration {{it}})"
 from s24 import _lib
 assert _lib.lib().s24_device_status(None) == 0, _lib.last_error()
 op.close()

@@ -147,6 +147,15 @@ class _FileBackend:
     def as_tensor(self, ptr, rows, cols, dtype):
         return self.maps[ptr // _KEY].view(dtype).view(rows, cols)
 
+    def copy_2d(self, dst, dst_pitch, src, src_pitch, width_bytes, rows, stream):
+        """pitched block copy between two mapped files (what the copy engines do between GPUs)"""
+        dk, doff = divmod(dst, _KEY)
+        sk, soff = divmod(src, _KEY)
+        d = self.maps[dk].view(torch.uint8)
+        s_ = self.maps[sk].view(torch.uint8)
+        for r in range(rows):
+            d[doff + r * dst_pitch:doff + r * dst_pitch + width_bytes] = s_[soff + r * src_pitch:soff + r * src_pitch + width_bytes]
+
 
 def _fused_worker(rank, world, port, result_dir):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -178,6 +187,21 @@ def _fused_worker(rank, world, port, result_dir):
             assert C.shape == (M, N) and C.dtype == torch.bfloat16
             assert torch.equal(C, want), f"iteration {it}"
         assert len(op._peer.ptrs) == world and op._peer.ptrs[rank] == op._peer._own
+        # replicated="copy": the product lands in this rank's copy in row panels, each pushed to the peers as a
+        # pitched block; same buffer, same fences
+        def fake_spmm(vals, meta_tc, Bs, out=None):
+            c = (vals.float() @ Bs.float()).to(vals.dtype)
+            if out is None:
+                return c
+            out.copy_(c)
+            return out
+        op.spmm_fn = fake_spmm
+        op._meta_rows = lambda r0, r1: None
+        for it in range(2):
+            B = torch.randn(K, N).to(torch.bfloat16)
+            want = (A.float() @ B.float()).to(torch.bfloat16)
+            C = op(B[:, n0:n1].contiguous(), n_total=N, replicated="copy", panels=2)
+            assert torch.equal(C, want), f"copy mode, iteration {it}"
         op.close()
         assert op._peer is None and not backend.maps       # every mapping released
         with open(os.path.join(result_dir, f"fused_ok_{rank}"), "w") as f:
