@@ -468,23 +468,23 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                     meta[c] = m;
                 };
+                // Software pipeline over 32-column chunks: the load of chunk c+1 is in flight while chunk c
+                // is ranked, and tensor memory goes back to the MMA warp as soon as the last load has
+                // landed, before the last chunk is ranked and before anything is stored.
+                uint32_t rbuf[2][32];
+                tc_ld_32x32b_x32(tacc, rbuf[0]);
 #pragma unroll
-                for (int c2 = 0; c2 < NPAIR; ++c2) {
-                    uint32_t r[64];
-                    tc_ld_32x32b_x64(tacc + (uint32_t)(c2 * 64), r);
+                for (int c = 0; c < NCH; ++c) {
                     tc_wait_ld();
-                    prune_chunk(r, 2 * c2);
-                    prune_chunk(r + 32, 2 * c2 + 1);
+                    if (c + 1 < NCH) {
+                        tc_ld_32x32b_x32(tacc + (uint32_t)((c + 1) * 32), rbuf[(c + 1) & 1]);
+                    } else {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+                    }
+                    prune_chunk(rbuf[c & 1], c);
                 }
-                if constexpr (NCH % 2 == 1) {
-                    uint32_t r[32];
-                    tc_ld_32x32b_x32(tacc + (uint32_t)((NCH - 1) * 32), r);
-                    tc_wait_ld();
-                    prune_chunk(r, NCH - 1);
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
 
                 const bool row_ok = row < p.M;
                 if (row_ok) {
