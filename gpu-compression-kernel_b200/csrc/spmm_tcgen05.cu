@@ -10,13 +10,17 @@
 // Design (one CTA, or a CTA pair working as one tile engine):
 //   * persistent grid: one CTA (pair) per SM (pair), tiles walked in groups of 8 M-tiles
 //     swept along N so that B tiles stay in L2;
-//   * warp 0: TMA producer.  Per k-block of 128 it loads A values (128 rows x 64 values,
-//     128-byte swizzle), this CTA's part of B (128 rows x BN_CTA columns as 64-column
-//     swizzled atoms) and one 2 KB metadata record into a STAGES-deep shared-memory ring;
-//   * warp 1: MMA issuer (one elected lane).  Per stage: tcgen05.cp moves the metadata
-//     record into 4 TMEM columns, then four tcgen05.mma.sp (K = 32 each) accumulate into
-//     TMEM; tcgen05.commit releases the stage and, after the last k-block, publishes the
-//     accumulator;
+//   * warp 0: TMA producer.  Two shared-memory rings with barriers of their own: the A ring
+//     holds units of one 128-row sub-tile x one k-block of 128 (A values: 128 rows x 64 values,
+//     128-byte swizzle, plus the 2 KB metadata record), the B ring units of one k-block of this
+//     CTA's part of B (128 rows x BN_CTA columns as 64-column swizzled atoms).  A k-block
+//     consumes MT units of A and one of B; separate rings let a sub-tile's A unit go back to the
+//     producer as soon as its own MMAs are done and keep more bytes in flight than whole
+//     (A + B) stages of the same total size would;
+//   * warp 1: MMA issuer (one elected lane).  Per k-block and sub-tile: tcgen05.cp moves the
+//     metadata record into 4 TMEM columns, then four tcgen05.mma.sp (K = 32 each) accumulate
+//     into TMEM; tcgen05.commit releases the A unit, after the last sub-tile the B unit and,
+//     after the last k-block, publishes that sub-tile's accumulator;
 //   * warps 2-9: epilogue, two warps per 32-lane TMEM quadrant (they split the tile's columns,
 //     or take one row sub-tile each).  One accumulator row per thread: wide tcgen05.ld
 //     (128 / 64 / 32 columns per round trip), convert, 32-byte stores issued as the data
@@ -36,11 +40,19 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
-#ifndef S24_B_TAIL_BOX
-#define S24_B_TAIL_BOX 1
+// ring depths of the 512 x 224 tile: 7 A units (3.5 k-blocks) and 3 B units fill the 227 KB
+#ifndef S24_NA_224
+#define S24_NA_224 7
 #endif
-#ifndef S24_EARLY_RELEASE
-#define S24_EARLY_RELEASE 1
+#ifndef S24_NB_224
+#define S24_NB_224 3
+#endif
+// ring depths of the 256 x 256 tile
+#ifndef S24_NA_256
+#define S24_NA_256 4
+#endif
+#ifndef S24_NB_256
+#define S24_NB_256 4
 #endif
 
 namespace s24 {
@@ -58,7 +70,7 @@ constexpr int kThreads = 320;       // producer warp, MMA warp, 8 epilogue warps
 // then K-major in shared memory like A's, loaded as two 64-wide K atoms per stage.
 // SCATTER: the epilogue stores every C tile to several destinations (this GPU's and its peers'
 // copies of a replicated result) through a shared-memory transpose that makes the stores whole lines.
-template <int G, int BN, int STAGES, bool PRUNE_OUT = false, int MT = 1, bool BT = false, bool SCATTER = false>
+template <int G, int BN, int NA, int NB, bool PRUNE_OUT = false, int MT = 1, bool BT = false, bool SCATTER = false>
 struct GemmCfg {
     static constexpr bool kPruneOut = PRUNE_OUT;
     static constexpr bool kBT = BT;
@@ -69,30 +81,32 @@ struct GemmCfg {
     static constexpr int kG = G;
     static constexpr int kBN = BN;
     static constexpr int kMT = MT;
-    static constexpr int kStages = STAGES;
+    static constexpr int kNA = NA;                              // A ring: units of (sub-tile, k-block)
+    static constexpr int kNB = NB;                              // B ring: units of one k-block
     static constexpr int kTileRows = kRowsPerCta * G * MT;
     static constexpr int kBNCta = BN / G;                       // B columns this CTA feeds to the MMA
     static constexpr int kASubBytes = kRowsPerCta * 128;        // 128 rows x 64 values x 2 B
-    static constexpr int kABytes = MT * kASubBytes;
     static constexpr int kBAtomBytes = kBlockK * 128;           // 128 k-rows x 64 columns x 2 B
-    static constexpr int kBAtoms = (kBNCta + 63) / 64;          // loaded as whole 64-column atoms
-    static constexpr int kBBytes = kBAtoms * kBAtomBytes;      // shared-memory footprint of a B stage
+    static constexpr int kBAtoms = (kBNCta + 63) / 64;          // 64-column atoms, the last one possibly narrower
+    static constexpr int kBBytes = kBAtoms * kBAtomBytes;      // shared-memory footprint of a B unit
     static constexpr int kBtAtomBytes = kBNCta * 128;           // transposed B: N rows x 64 k-values x 2 B
     // columns of the last atom that belong to this CTA: loaded with a narrower box of its own so
     // that no column outside the tile is fetched (0 = the last atom is whole)
-    static constexpr int kBTailCols = S24_B_TAIL_BOX ? (kBNCta % 64) : 0;
+    static constexpr int kBTailCols = kBNCta % 64;
     static constexpr int kBLoadBytes = BT ? 2 * kBtAtomBytes
                                           : (kBTailCols ? (kBAtoms - 1) * kBAtomBytes + kBlockK * kBTailCols * 2 : kBBytes);
     static constexpr int kESubBytes = 2048;
-    static constexpr int kEBytes = MT * kESubBytes;
-    static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;
-    static constexpr int kStageTxBytes = kABytes + kBLoadBytes + kEBytes;
+    static constexpr int kATxBytes = kASubBytes + kESubBytes;   // bytes one A unit's copies deliver
     static constexpr int kAccCols = BN * MT;                    // one accumulator set
     static constexpr int kAccStages = (kAccCols >= 256) ? 1 : 2;
+    static constexpr int kAccBars = kAccStages * MT;            // each sub-tile's accumulator has barriers of its own
     static constexpr int kECol0 = kAccStages * kAccCols;        // metadata columns follow the accumulators
-    static constexpr int kSmemBytes = STAGES * kStageBytes + kScatterBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kBarrierBytes = 8 * (2 * NA + 2 * NB + 2 * kAccBars) + 16;
+    static constexpr int kSmemBytes = NA * (kASubBytes + kESubBytes) + NB * kBBytes + kScatterBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static_assert(!SCATTER || (MT == 1 && BN == 256 && !PRUNE_OUT), "the scatter epilogue is written for 128-column warp slices");
-    static_assert(kECol0 + 4 * MT * STAGES <= (int)kTmemCols, "tensor memory budget");
+    static_assert(kECol0 + 4 * NA <= (int)kTmemCols, "tensor memory budget");
+    static_assert(NA >= 2 * MT && NB >= 2, "at least two k-blocks in each ring");
+    static_assert(kBarrierBytes <= 256, "barrier block");
     static_assert(kBNCta % 8 == 0 && BN % (16 * G) == 0, "MMA N granularity");
     static_assert(BN % 32 == 0 && (BN / (MT == 2 ? 1 : 2)) % 32 == 0, "the epilogues work in 32-column chunks");
     static_assert(kSmemBytes <= 232448, "shared memory budget (227 KB per CTA)");
@@ -119,23 +133,27 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 {
     constexpr int G = Cfg::kG;
     constexpr int BN = Cfg::kBN;
-    constexpr int STAGES = Cfg::kStages;
+    constexpr int NA = Cfg::kNA;
+    constexpr int NB = Cfg::kNB;
     constexpr int ACC = Cfg::kAccStages;
     constexpr int MT = Cfg::kMT;
+    constexpr int ACCB = Cfg::kAccBars;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t smem_a = smem_base;
-    const uint32_t smem_b = smem_a + STAGES * Cfg::kABytes;
-    const uint32_t smem_e = smem_b + STAGES * Cfg::kBBytes;
-    const uint32_t smem_scatter = smem_e + STAGES * Cfg::kEBytes;
+    const uint32_t smem_b = smem_a + NA * Cfg::kASubBytes;
+    const uint32_t smem_e = smem_b + NB * Cfg::kBBytes;
+    const uint32_t smem_scatter = smem_e + NA * Cfg::kESubBytes;
     const uint32_t bars = smem_scatter + Cfg::kScatterBytes;
-    // barrier block: full[STAGES], empty[STAGES], acc_full[ACC], acc_empty[ACC], tmem slot, abort flag
-    const uint32_t bar_full = bars;
-    const uint32_t bar_empty = bar_full + 8 * STAGES;
-    const uint32_t bar_acc_full = bar_empty + 8 * STAGES;
-    const uint32_t bar_acc_empty = bar_acc_full + 8 * ACC;
-    const uint32_t tmem_slot = bar_acc_empty + 8 * ACC;
+    // barrier block: a_full[NA], a_empty[NA], b_full[NB], b_empty[NB], acc_full[ACCB], acc_empty[ACCB], tmem slot, abort flag
+    const uint32_t bar_a_full = bars;
+    const uint32_t bar_a_empty = bar_a_full + 8 * NA;
+    const uint32_t bar_b_full = bar_a_empty + 8 * NA;
+    const uint32_t bar_b_empty = bar_b_full + 8 * NB;
+    const uint32_t bar_acc_full = bar_b_empty + 8 * NB;
+    const uint32_t bar_acc_empty = bar_acc_full + 8 * ACCB;
+    const uint32_t tmem_slot = bar_acc_empty + 8 * ACCB;
     const uint32_t abort_addr = tmem_slot + 8;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     volatile uint32_t* tmem_slot_ptr =
@@ -155,13 +173,17 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const int kblocks = (p.K + kBlockK - 1) / kBlockK;   // a last block of 64 reads zeros beyond K
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1);   // one arrive (the leader's producer) + both CTAs' bytes
-            mbar_init(bar_empty + 8 * s, 1);
+        for (int s = 0; s < NA; ++s) {
+            mbar_init(bar_a_full + 8 * s, 1);   // one arrive (the leader's producer) + both CTAs' bytes
+            mbar_init(bar_a_empty + 8 * s, 1);
         }
-        for (int a = 0; a < ACC; ++a) {
+        for (int s = 0; s < NB; ++s) {
+            mbar_init(bar_b_full + 8 * s, 1);
+            mbar_init(bar_b_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < ACCB; ++a) {
             mbar_init(bar_acc_full + 8 * a, 1);
-            mbar_init(bar_acc_empty + 8 * a, 8 * G);   // every epilogue warp of every CTA
+            mbar_init(bar_acc_empty + 8 * a, (8 / MT) * G);   // the epilogue warps of every CTA that drain this sub-tile
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -179,8 +201,8 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (elect_one()) {
-            int s = 0;
-            uint32_t phase = 0;
+            int sa = 0, sb = 0;
+            uint32_t pha = 0, phb = 0;
             bool stopped = false;
             for (int t = unit; t < num_tiles && !stopped && !*abort_flag; t += num_units) {
                 int tm, tn;
@@ -188,37 +210,30 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 // sub-tile m of this CTA: rows row0 + m * 128 * G .. + 127
                 const int row0 = tm * Cfg::kTileRows + (int)cta_rank * kRowsPerCta;
                 const int col0 = tn * BN + (int)cta_rank * Cfg::kBNCta;
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    // self-test of the time-out path: stop feeding the ring; nothing is left in flight
-                    if (p.selftest_stop_after_kblocks > 0 && kb >= p.selftest_stop_after_kblocks) {
-                        stopped = true;
-                        break;
+                // The leader announces the bytes of both CTAs on its own barrier; the peer's copies
+                // complete on the leader's barrier too (their bytes may run ahead of the
+                // announcement, which the transaction count tolerates).
+                auto load_a = [&](int kb, int m) -> bool {
+                    if (!mbar_wait(bar_a_empty + 8 * sa, pha ^ 1u, p.wait_limit_ns)) return false;
+                    const uint32_t full = (G == 2) ? mapa(bar_a_full + 8 * sa, 0) : (bar_a_full + 8 * sa);
+                    if (leader) mbar_arrive_expect_tx(bar_a_full + 8 * sa, (uint32_t)(G * Cfg::kATxBytes));
+                    const int rows = row0 + m * kRowsPerCta * G;
+                    const int rec = (rows / kRowsPerCta) * kblocks + kb;
+                    if (G == 2) {
+                        tma_load_2d_pair(smem_a + sa * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
+                        tma_load_2d_pair(smem_e + sa * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
+                    } else {
+                        tma_load_2d(smem_a + sa * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
+                        tma_load_2d(smem_e + sa * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
                     }
-                    if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u, p.wait_limit_ns)) {
-                        report_timeout(p.status, abort_flag, 1);
-                        break;
-                    }
-                    const uint32_t full = (G == 2) ? mapa(bar_full + 8 * s, 0) : (bar_full + 8 * s);   // the leader's barrier
-                    // the leader announces the bytes of both CTAs; the peer's copies complete on the
-                    // leader's barrier too (its byte count may run ahead of the announcement, which
-                    // the transaction count tolerates)
-                    if (leader)
-                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)(G * Cfg::kStageTxBytes));
-                    const uint32_t a_dst = smem_a + s * Cfg::kABytes;
-                    const uint32_t b_dst = smem_b + s * Cfg::kBBytes;
-                    const uint32_t e_dst = smem_e + s * Cfg::kEBytes;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const int rows = row0 + m * kRowsPerCta * G;
-                        const int rec = (rows / kRowsPerCta) * kblocks + kb;
-                        if (G == 2) {
-                            tma_load_2d_pair(a_dst + m * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
-                            tma_load_2d_pair(e_dst + m * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
-                        } else {
-                            tma_load_2d(a_dst + m * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
-                            tma_load_2d(e_dst + m * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
-                        }
-                    }
+                    if (++sa == NA) { sa = 0; pha ^= 1u; }
+                    return true;
+                };
+                auto load_b = [&](int kb) -> bool {
+                    if (!mbar_wait(bar_b_empty + 8 * sb, phb ^ 1u, p.wait_limit_ns)) return false;
+                    const uint32_t full = (G == 2) ? mapa(bar_b_full + 8 * sb, 0) : (bar_b_full + 8 * sb);
+                    if (leader) mbar_arrive_expect_tx(bar_b_full + 8 * sb, (uint32_t)(G * Cfg::kBLoadBytes));
+                    const uint32_t b_dst = smem_b + sb * Cfg::kBBytes;
                     if constexpr (Cfg::kBT) {
                         // transposed B: two boxes of (64 k-values x kBNCta rows of N)
 #pragma unroll
@@ -236,7 +251,24 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             else tma_load_2d(b_dst + i * Cfg::kBAtomBytes, map, col0 + 64 * i, kb * kBlockK, full);
                         }
                     }
-                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                    if (++sb == NB) { sb = 0; phb ^= 1u; }
+                    return true;
+                };
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    // self-test of the time-out path: stop feeding the rings; nothing is left in flight
+                    if (p.selftest_stop_after_kblocks > 0 && kb >= p.selftest_stop_after_kblocks) {
+                        stopped = true;
+                        break;
+                    }
+                    // in the order the MMA warp needs them: first sub-tile's A, B, remaining sub-tiles' A
+                    bool ok = load_a(kb, 0) && load_b(kb);
+#pragma unroll
+                    for (int m = 1; m < MT; ++m) ok = ok && load_a(kb, m);
+                    if (!ok) {
+                        report_timeout(p.status, abort_flag, 1);
+                        stopped = true;
+                        break;
+                    }
                 }
             }
         }
@@ -244,57 +276,67 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (leader && elect_one()) {
             const uint32_t idesc = make_idesc_sp_f16(p.bf16, kRowsPerCta * G, BN, Cfg::kBT ? 0 : 1);
-            int s = 0, a = 0;
-            uint32_t phase = 0, acc_phase = 0;
-            for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
-                if (!mbar_wait(bar_acc_empty + 8 * a, acc_phase ^ 1u, p.wait_limit_ns)) {
-                    report_timeout(p.status, abort_flag, 3);
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(a * Cfg::kAccCols);
-                bool ok = true;
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(bar_full + 8 * s, phase, p.wait_limit_ns)) {
+            int sa = 0, sb = 0, a = 0;
+            uint32_t pha = 0, phb = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = unit; t < num_tiles && ok && !*abort_flag; t += num_units) {
+                for (int kb = 0; kb < kblocks && ok; ++kb) {
+                    if (!mbar_wait(bar_b_full + 8 * sb, phb, p.wait_limit_ns)) {
                         report_timeout(p.status, abort_flag, 2);
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
-                    const uint32_t e_cols = tmem_base + (uint32_t)(Cfg::kECol0 + 4 * MT * s);
-                    // metadata records: 128 rows of 16 bytes, 8-row core matrices 128 bytes apart
-#pragma unroll
-                    for (int m = 0; m < MT; ++m)
-                        tc_cp_128x128b<G>(e_cols + 4 * m,
-                                          make_smem_desc(smem_e + s * Cfg::kEBytes + m * Cfg::kESubBytes, 128, 128, kSwizzleNone));
-                    // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
-                    const uint64_t adesc = make_smem_desc(smem_a + s * Cfg::kABytes, 16, 1024, kSwizzle128B);
                     // B: N-major, 128-byte swizzle; 64-column atoms kBAtomBytes apart (leading),
                     // 8-k-row groups 1024 bytes apart (stride)
-                    const uint64_t bdesc = make_smem_desc(smem_b + s * Cfg::kBBytes, Cfg::kBAtomBytes, 1024, kSwizzle128B);
+                    const uint64_t bdesc = make_smem_desc(smem_b + sb * Cfg::kBBytes, Cfg::kBAtomBytes, 1024, kSwizzle128B);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // K = 32 per instruction: 32 bytes further along A's rows, 32 k-rows (4096 B) into B,
-                        // metadata column j (even column address + selector bit); the sub-tiles reuse
-                        // the same B slice back to back
-                        // transposed B is K-major like A: 64 bytes per K = 32 step inside a 128-byte row,
-                        // the second pair of steps in the second 64-wide K atom
-                        const uint64_t bstep = Cfg::kBT
-                            ? make_smem_desc(smem_b + s * Cfg::kBBytes + (j >> 1) * Cfg::kBtAtomBytes + (j & 1) * 64, 16, 1024, kSwizzle128B)
-                            : bdesc + (uint64_t)(j * 256);
+                    for (int m = 0; m < MT; ++m) {
+                        const int ab = a * MT + m;   // this sub-tile's accumulator
+                        if (kb == 0) {
+                            if (!mbar_wait(bar_acc_empty + 8 * ab, acc_phase ^ 1u, p.wait_limit_ns)) {
+                                report_timeout(p.status, abort_flag, 3);
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!mbar_wait(bar_a_full + 8 * sa, pha, p.wait_limit_ns)) {
+                            report_timeout(p.status, abort_flag, 2);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t tmem_d = tmem_base + (uint32_t)(a * Cfg::kAccCols + m * BN);
+                        const uint32_t e_cols = tmem_base + (uint32_t)(Cfg::kECol0 + 4 * sa);
+                        // metadata record: 128 rows of 16 bytes, 8-row core matrices 128 bytes apart
+                        tc_cp_128x128b<G>(e_cols, make_smem_desc(smem_e + sa * Cfg::kESubBytes, 128, 128, kSwizzleNone));
+                        // A: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+                        const uint64_t adesc = make_smem_desc(smem_a + sa * Cfg::kASubBytes, 16, 1024, kSwizzle128B);
 #pragma unroll
-                        for (int m = 0; m < MT; ++m)
-                            tc_mma_sp_f16<G>(tmem_d + (uint32_t)(m * BN), adesc + (uint64_t)(m * (Cfg::kASubBytes >> 4) + j * 2),
-                                             bstep, idesc | (uint32_t)(j & 1),
-                                             e_cols + (uint32_t)(4 * m + (j & 2)), (kb | j) != 0 ? 1u : 0u);
+                        for (int j = 0; j < 4; ++j) {
+                            // K = 32 per instruction: 32 bytes further along A's rows, 32 k-rows (4096 B) into B,
+                            // metadata column j (even column address + selector bit).
+                            // Transposed B is K-major like A: 64 bytes per K = 32 step inside a 128-byte row,
+                            // the second pair of steps in the second 64-wide K atom.
+                            const uint64_t bstep = Cfg::kBT
+                                ? make_smem_desc(smem_b + sb * Cfg::kBBytes + (j >> 1) * Cfg::kBtAtomBytes + (j & 1) * 64, 16, 1024, kSwizzle128B)
+                                : bdesc + (uint64_t)(j * 256);
+                            tc_mma_sp_f16<G>(tmem_d, adesc + (uint64_t)(j * 2), bstep, idesc | (uint32_t)(j & 1),
+                                             e_cols + (uint32_t)(j & 2), (kb | j) != 0 ? 1u : 0u);
+                        }
+                        // the A unit goes back to the producer once these MMAs have read it
+                        if (G == 2) tc_commit_pair(bar_a_empty + 8 * sa, 3);
+                        else tc_commit<1>(bar_a_empty + 8 * sa);
+                        if (++sa == NA) { sa = 0; pha ^= 1u; }
+                        if (kb == kblocks - 1) {   // this sub-tile's accumulator is complete
+                            if (G == 2) tc_commit_pair(bar_acc_full + 8 * ab, 3);
+                            else tc_commit<1>(bar_acc_full + 8 * ab);
+                        }
                     }
-                    if (G == 2) tc_commit_pair(bar_empty + 8 * s, 3);
-                    else tc_commit<1>(bar_empty + 8 * s);
-                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                    if (!ok) break;
+                    if (G == 2) tc_commit_pair(bar_b_empty + 8 * sb, 3);
+                    else tc_commit<1>(bar_b_empty + 8 * sb);
+                    if (++sb == NB) { sb = 0; phb ^= 1u; }
                 }
-                if (!ok) break;
-                if (G == 2) tc_commit_pair(bar_acc_full + 8 * a, 3);
-                else tc_commit<1>(bar_acc_full + 8 * a);
                 if (++a == ACC) { a = 0; acc_phase ^= 1u; }
             }
         }
@@ -308,11 +350,12 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         const int chalf = (MT == 2) ? 0 : half;
         int a = 0;
         uint32_t acc_phase = 0;
-        const uint32_t acc_empty_leader = (G == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
+        // each sub-tile's accumulator has its own full / empty pair: this warp's is number a * MT + sub
+        const uint32_t acc_empty_leader = ((G == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty) + 8 * (uint32_t)sub;
         for (int t = unit; t < num_tiles && !*abort_flag; t += num_units) {
             int tm, tn;
             tile_coords(t, num_m, num_n, tm, tn);
-            if (!mbar_wait(bar_acc_full + 8 * a, acc_phase, p.wait_limit_ns)) {
+            if (!mbar_wait(bar_acc_full + 8 * (a * MT + sub), acc_phase, p.wait_limit_ns)) {
                 if (lane == 0) report_timeout(p.status, abort_flag, 4);
                 break;
             }
@@ -331,7 +374,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 tc_wait_ld();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * (a * MT));
                 const uint32_t stg = smem_scatter + (uint32_t)(warp - 2) * (uint32_t)Cfg::kScatterWarpBytes +
                                      (uint32_t)lane * (uint32_t)Cfg::kScatterPitch;
                 bulk_wait_read();   // the previous tile's copies have read this slice
@@ -372,7 +415,6 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 };
                 static_assert(CW % 32 == 0, "epilogue works in 32-column pieces");
-#if S24_EARLY_RELEASE
                 uint32_t q[CW / 2];
                 auto pack = [&](const uint32_t* r, int c_off, int width) {
 #pragma unroll
@@ -409,47 +451,9 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 // every accumulator column of this warp has been read: hand TMEM back to the MMA warp
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * (a * MT));
 #pragma unroll
                 for (int i = 0; i < CW / 16; ++i) store16(q + 8 * i, 16 * i);
-#else
-                auto emit = [&](const uint32_t* r, int c_off, int width) {
-#pragma unroll
-                    for (int i = 0; i < width / 16; ++i) {
-                        uint32_t q[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            q[j] = pack2(__uint_as_float(r[16 * i + 2 * j]), __uint_as_float(r[16 * i + 2 * j + 1]), p.bf16);
-                        store16(q, c_off + 16 * i);
-                    }
-                };
-                int done = 0;
-#pragma unroll
-                for (int k = 0; k < CW / 128; ++k) {
-                    uint32_t r[128];
-                    tc_ld_32x32b_x128(tacc + (uint32_t)done, r);
-                    tc_wait_ld();
-                    emit(r, done, 128);
-                    done += 128;
-                }
-                if constexpr ((CW % 128) >= 64) {
-                    uint32_t r[64];
-                    tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
-                    tc_wait_ld();
-                    emit(r, done, 64);
-                    done += 64;
-                }
-                if constexpr ((CW % 64) >= 32) {
-                    uint32_t r[32];
-                    tc_ld_32x32b_x32(tacc + (uint32_t)done, r);
-                    tc_wait_ld();
-                    emit(r, done, 32);
-                    done += 32;
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
-#endif
             } else {
                 // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
                 constexpr int NCH = CW / 32;     // 32-column chunks of this warp
@@ -481,7 +485,7 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * a);
+                        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * (a * MT));
                     }
                     prune_chunk(rbuf[c & 1], c);
                 }
@@ -730,7 +734,7 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     g.p.selftest_stop_after_kblocks = selftest_stop_after_kblocks;
     g.p.n_dst = dsts ? n_dst : 0;
     for (int d = 0; d < 8; ++d) g.p.dst[d] = (dsts && d < n_dst) ? dsts[d] : nullptr;
-    if (dsts != nullptr) return launch_cfg<GemmCfg<2, 256, 3, false, 1, false, true>>(g, stream);
+    if (dsts != nullptr) return launch_cfg<GemmCfg<2, 256, 3, 3, false, 1, false, true>>(g, stream);
     if (prune_out && c_meta_tc != nullptr && M % 128 != 0) {
         // the last 128-row record group is only partly written by the epilogue: give the rest a valid code
         int rc = check_cuda(cudaMemsetAsync(c_meta_tc, 0x44, s24_meta_tc_bytes(M, N), stream), "output metadata prefill");
@@ -763,20 +767,20 @@ static int run_spmm(const void* vals, const void* meta_tc, const void* B, void* 
     if (bm == 0) bm = (M % 256 == 0 || M > 1024) ? 256 : 128;
     if (bn == 0) bn = (bm == 512) ? 224 : ((bm == 256 && N >= 256) ? 256 : 128);
     if (prune_out) {
-        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, true, 2>>(g, stream);
-        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, true>>(g, stream);
-        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, true>>(g, stream);
-        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, true>>(g, stream);
+        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, S24_NA_224, S24_NB_224, true, 2>>(g, stream);
+        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, S24_NA_256, S24_NB_256, true>>(g, stream);
+        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, 6, true>>(g, stream);
+        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, 4, true>>(g, stream);
     } else if (bt) {
-        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, false, 2, true>>(g, stream);
-        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4, false, 1, true>>(g, stream);
-        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, false, 1, true>>(g, stream);
-        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, false, 1, true>>(g, stream);
+        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, S24_NA_224, S24_NB_224, false, 2, true>>(g, stream);
+        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, S24_NA_256, S24_NB_256, false, 1, true>>(g, stream);
+        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, 6, false, 1, true>>(g, stream);
+        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, 4, false, 1, true>>(g, stream);
     } else {
-        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, 3, false, 2>>(g, stream);
-        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, 4>>(g, stream);
-        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6>>(g, stream);
-        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4>>(g, stream);
+        if (bm == 512 && bn == 224) return launch_cfg<GemmCfg<2, 224, S24_NA_224, S24_NB_224, false, 2>>(g, stream);
+        if (bm == 256 && bn == 256) return launch_cfg<GemmCfg<2, 256, S24_NA_256, S24_NB_256>>(g, stream);
+        if (bm == 256 && bn == 128) return launch_cfg<GemmCfg<2, 128, 6, 6>>(g, stream);
+        if (bm == 128 && bn == 128) return launch_cfg<GemmCfg<1, 128, 4, 4>>(g, stream);
     }
     return fail(S24_ERR_UNSUPPORTED, "%s: no kernel for tile %d x %d (have 512x224, 256x256, 256x128, 128x128)", who, bm, bn);
 }
