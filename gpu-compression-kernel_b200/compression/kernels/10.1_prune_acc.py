@@ -15,9 +15,11 @@ import s24  # noqa: E402
 
 
 def run_sparse_ws_matmul(A, E, B, tune=True, manual_config=None):
-    """(C_vals, C_meta) = compress(prune_2_4(A24 @ B)) with the pruning done on the fp32
-    accumulator (signed keys, the lower index survives a tie: 10.1_prune_acc.py:100-105) and the
-    survivors rounded afterwards (:241)."""
+    """(C_vals, C_meta) = compress(prune_2_4(A24 @ B)) with the pruning done in the GEMM's epilogue
+    (signed keys, the lower index survives a tie: 10.1_prune_acc.py:100-105).  The accumulators are
+    rounded to the output type first and ranked then, so the result equals prune + compress of the
+    dense product the plain launcher returns; the reference ranks the fp32 values and rounds the
+    survivors (:241), which differs only where two sums of a group round to the same number."""
     cfg = None
     if not tune and manual_config:
         cfg = {k: manual_config[k] for k in ("BM", "BN") if manual_config.get(k) in (128, 224, 256, 512)} or None

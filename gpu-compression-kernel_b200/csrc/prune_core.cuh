@@ -162,6 +162,9 @@ struct PairOut {
     uint32_t v0, v1, codes;
 };
 
+// the same from given "stored" flags m0, m1, m3 (0xFFFF / 0 per half) instead of non-zero flags
+S24_HD PairOut encode_pair_flags(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3, uint32_t m0, uint32_t m1, uint32_t m3);
+
 template <int DT, bool ZERO_SIGN_CLEAR>
 S24_HD PairOut encode_pair(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3)
 {
@@ -172,6 +175,11 @@ S24_HD PairOut encode_pair(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3)
         p2 &= nz2<DT>(p2);
         p3 &= m3;
     }
+    return encode_pair_flags(p0, p1, p2, p3, m0, m1, m3);
+}
+
+S24_HD PairOut encode_pair_flags(uint32_t p0, uint32_t p1, uint32_t p2, uint32_t p3, uint32_t m0, uint32_t m1, uint32_t m3)
+{
     const uint32_t both = m0 & m1;
     const uint32_t none_or_m3 = ~(m0 | m1) | m3;
     PairOut o;
@@ -308,6 +316,25 @@ S24_HD uint32_t prune_compress_8(uint32_t in0, uint32_t in1, uint32_t in2, uint3
     out_lo = byte_perm(o.v0, o.v1, 0x5410);
     out_hi = byte_perm(o.v0, o.v1, 0x7632);
     // codes = lo + hi * 2^16; times (2^24 + 2^12) puts lo at bits 24-27 and hi at bits 28-31
+    return o.codes * 0x01001000u;
+}
+
+// The same for a fused GEMM epilogue (compression/kernels/10.1_prune_acc.py:100-117): signed keys, the
+// lower index survives a tie, and the codes come from the keep masks themselves, so a surviving
+// exact zero is still recorded where it stands (the reference's kernel encodes from its mask, not
+// from non-zero flags).
+template <int DT>
+S24_HD uint32_t prune_compress_8_from_mask(uint32_t in0, uint32_t in1, uint32_t in2, uint32_t in3, uint32_t& out_lo,
+                                           uint32_t& out_hi)
+{
+    const uint32_t P0 = byte_perm(in0, in2, 0x5410), P1 = byte_perm(in0, in2, 0x7632);
+    const uint32_t P2 = byte_perm(in1, in3, 0x5410), P3 = byte_perm(in1, in3, 0x7632);
+    uint32_t k0, k1, k2, k3, tiebits;
+    keep_masks<DT, kModeSigned>(P0, P1, P2, P3, k0, k1, k2, k3, tiebits);
+    if (tiebits != 0) fix_tied_masks<DT, kModeSigned>(P0, P1, P2, P3, tiebits, kTieLower, k0, k1, k2, k3);
+    const PairOut o = encode_pair_flags(P0 & k0, P1 & k1, P2 & k2, P3 & k3, k0, k1, k3);
+    out_lo = byte_perm(o.v0, o.v1, 0x5410);
+    out_hi = byte_perm(o.v0, o.v1, 0x7632);
     return o.codes * 0x01001000u;
 }
 

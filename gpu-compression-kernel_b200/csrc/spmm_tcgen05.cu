@@ -36,6 +36,7 @@
 #include "s24_common.cuh"
 #include "sm100_ptx.cuh"
 #include "spmm_shared.cuh"
+#include "prune_core.cuh"
 
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -111,20 +112,6 @@ struct GemmCfg {
     static_assert(BN % 32 == 0 && (BN / (MT == 2 ? 1 : 2)) % 32 == 0, "the epilogues work in 32-column chunks");
     static_assert(kSmemBytes <= 232448, "shared memory budget (227 KB per CTA)");
 };
-
-// 2:4 prune of four fp32 accumulators along N, as the reference's fused epilogue does
-// (compression/kernels/10.1_prune_acc.py:100-117): signed keys, >= so the lower index survives
-// a tie, the two survivors in index order and the code derived from the keep mask.
-__device__ __forceinline__ uint32_t prune_group_f32(float a0, float a1, float a2, float a3, float& v0, float& v1)
-{
-    const bool c01 = a0 >= a1, c02 = a0 >= a2, c03 = a0 >= a3, c12 = a1 >= a2, c13 = a1 >= a3, c23 = a2 >= a3;
-    const bool b0 = (c01 && (c02 || c03)) || (c02 && c03);
-    const bool b1 = (!c01 && (c12 || c13)) || (c12 && c13);
-    const bool b2 = (!c02 && (!c12 || c23)) || (!c12 && c23);
-    v0 = b0 ? a0 : (b1 ? a1 : a2);
-    v1 = (b0 && b1) ? a1 : ((b2 && (b0 || b1)) ? a2 : a3);
-    return b0 ? (b1 ? 4u : (b2 ? 8u : 12u)) : (b1 ? (b2 ? 9u : 13u) : 14u);
-}
 
 template <class Cfg>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -393,13 +380,14 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         bulk_store(static_cast<uint16_t*>(p.dst[d]) + off, stg, (uint32_t)(ncols * 2));
                 }
                 bulk_commit();
-            } else if constexpr (!Cfg::kPruneOut) {
+            } else {
                 // Drain in as few round trips as possible: one tcgen05.ld per 128 (then 64 + 32)
                 // columns, round to 16 bits in registers, hand tensor memory back to the MMA warp and
                 // only then issue the stores (32 bytes per thread to rows that lie ldc apart, which
                 // the load/store unit takes a sector at a time): the next tile's main loop starts
-                // while this tile is still on its way to memory.
-                uint16_t* crow = static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
+                // while this tile is still on its way to memory.  The pruning epilogue does the same
+                // and ranks the rounded values after the release.
+                uint16_t* crow = Cfg::kPruneOut ? nullptr : static_cast<uint16_t*>(p.C) + row * p.ldc + col0;
                 const bool row_ok = row < p.M;
                 // 16 columns = 32 bytes = one full L2 sector per store when C allows it
                 const bool wide = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * 2)) & 31u) == 0;
@@ -452,91 +440,80 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * (a * MT));
+                if constexpr (!Cfg::kPruneOut) {
 #pragma unroll
-                for (int i = 0; i < CW / 16; ++i) store16(q + 8 * i, 16 * i);
-            } else {
-                // fused output prune: per 32 accumulator columns keep 16 values and 32 metadata bits
-                constexpr int NCH = CW / 32;     // 32-column chunks of this warp
-                constexpr int NPAIR = NCH / 2;   // pairs of chunks (64 columns, one load round trip)
-                uint32_t vals[CW / 4];           // packed 16-bit pairs: 8 registers per chunk
-                uint32_t meta[NCH];              // codes of 8 groups, group g in bits 4g..4g+3
-                auto prune_chunk = [&](const uint32_t* r, int c) {
-                    uint32_t m = 0;
-#pragma unroll
-                    for (int g4 = 0; g4 < 8; ++g4) {
-                        float v0, v1;
-                        const uint32_t code = prune_group_f32(__uint_as_float(r[4 * g4]), __uint_as_float(r[4 * g4 + 1]),
-                                                              __uint_as_float(r[4 * g4 + 2]), __uint_as_float(r[4 * g4 + 3]), v0, v1);
-                        vals[c * 8 + g4] = pack2(v0, v1, p.bf16);   // rounded after selection (10.1_prune_acc.py:241)
-                        m |= code << (4 * g4);
-                    }
-                    meta[c] = m;
-                };
-                // Software pipeline over 32-column chunks: the load of chunk c+1 is in flight while chunk c
-                // is ranked, and tensor memory goes back to the MMA warp as soon as the last load has
-                // landed, before the last chunk is ranked and before anything is stored.
-                uint32_t rbuf[2][32];
-                tc_ld_32x32b_x32(tacc, rbuf[0]);
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    tc_wait_ld();
-                    if (c + 1 < NCH) {
-                        tc_ld_32x32b_x32(tacc + (uint32_t)((c + 1) * 32), rbuf[(c + 1) & 1]);
-                    } else {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(acc_empty_leader + 8 * (a * MT));
-                    }
-                    prune_chunk(rbuf[c & 1], c);
-                }
-
-                const bool row_ok = row < p.M;
-                if (row_ok) {
-                    uint16_t* vrow = static_cast<uint16_t*>(p.c_vals) + row * (int64_t)(p.N / 2) + col0 / 2;
+                    for (int i = 0; i < CW / 16; ++i) store16(q + 8 * i, 16 * i);
+                } else {
+                    // Fused output prune (compression/kernels/10.1_prune_acc.py:88-154): per 32 columns keep 16
+                    // values and 32 metadata bits.  The groups are ranked on the accumulators as rounded to
+                    // the output type, with the packed 16-bit SIMD arithmetic of the stand-alone
+                    // prune+compress kernel (signed keys, the lower index survives a tie, codes from the
+                    // keep mask): the result is exactly compress(prune(C)) of the C the plain kernel
+                    // would have stored, and differs from a ranking of the unrounded fp32 sums only where
+                    // the second and third largest of a group round to the same 16-bit value.
+                    constexpr int NCH = CW / 32;     // 32-column chunks of this warp
+                    constexpr int NPAIR = NCH / 2;   // pairs of chunks
+                    uint32_t vals[CW / 4];           // packed 16-bit pairs: 8 registers per chunk
+                    uint32_t meta[NCH];              // codes of 8 groups, group g in bits 4g..4g+3
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
-                        if (col0 + c * 32 < p.N) {
-                            *reinterpret_cast<uint4*>(vrow + c * 16) =
-                                make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
-                            *reinterpret_cast<uint4*>(vrow + c * 16 + 8) =
-                                make_uint4(vals[c * 8 + 4], vals[c * 8 + 5], vals[c * 8 + 6], vals[c * 8 + 7]);
+                        uint32_t code[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {   // 8 columns = two groups at a time
+                            const uint32_t* in = q + 16 * c + 4 * i;
+                            code[i] = p.bf16 ? prune_compress_8_from_mask<kBf16>(in[0], in[1], in[2], in[3], vals[c * 8 + 2 * i], vals[c * 8 + 2 * i + 1])
+                                             : prune_compress_8_from_mask<kFp16>(in[0], in[1], in[2], in[3], vals[c * 8 + 2 * i], vals[c * 8 + 2 * i + 1]);
+                        }
+                        meta[c] = gather_code_bytes(code[0], code[1], code[2], code[3]);
+                    }
+
+                    if (row_ok) {
+                        uint16_t* vrow = static_cast<uint16_t*>(p.c_vals) + row * (int64_t)(p.N / 2) + col0 / 2;
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c) {
+                            if (col0 + c * 32 < p.N) {
+                                *reinterpret_cast<uint4*>(vrow + c * 16) =
+                                    make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
+                                *reinterpret_cast<uint4*>(vrow + c * 16 + 8) =
+                                    make_uint4(vals[c * 8 + 4], vals[c * 8 + 5], vals[c * 8 + 6], vals[c * 8 + 7]);
+                            }
                         }
                     }
-                }
-                // Metadata words pair row r (low half) with row r+8 (high half): lanes l and l^8 of this
-                // warp.  A 32-column chunk gives two words (16 columns each).  Chunks are handled in
-                // pairs: the lane with bit 3 clear assembles the two words of the first chunk, its
-                // partner those of the second, so each writes 8 adjacent bytes; an odd last chunk is
-                // written by the lower lanes alone.
-                const bool upper = (lane & 8) != 0;
-                const int m0 = lane & 7;
-                const int64_t row16 = row >> 4;
-                auto write_words = [&](uint32_t w0, uint32_t w1, int ncol) {   // ncol: first column of w0
-                    if (!row_ok || ncol >= p.N) return;
-                    const int cidx = ncol >> 4;                                  // logical metadata column of w0
-                    if (p.c_meta_ref != nullptr) {
-                        uint32_t* e = p.c_meta_ref + row16 * (int64_t)(p.N / 2) + (cidx >> 2) * 32 + m0 * 4 + (cidx & 3);
-                        *reinterpret_cast<uint2*>(e) = make_uint2(w0, w1);
-                    }
-                    if (p.c_meta_tc != nullptr) {
-                        const int64_t t128 = row >> 7;
-                        const int m2 = (int)((row >> 4) & 7);
-                        const int kb = cidx >> 3, j = (cidx & 7) >> 1;
-                        uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)((p.N + 127) >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
-                        rec[0] = w0;
-                        rec[32] = w1;
-                    }
-                };
+                    // Metadata words pair row r (low half) with row r+8 (high half): lanes l and l^8 of this
+                    // warp.  A 32-column chunk gives two words (16 columns each).  Chunks are handled in
+                    // pairs: the lane with bit 3 clear assembles the two words of the first chunk, its
+                    // partner those of the second, so each writes 8 adjacent bytes; an odd last chunk is
+                    // written by the lower lanes alone.
+                    const bool upper = (lane & 8) != 0;
+                    const int m0 = lane & 7;
+                    const int64_t row16 = row >> 4;
+                    auto write_words = [&](uint32_t w0, uint32_t w1, int ncol) {   // ncol: first column of w0
+                        if (!row_ok || ncol >= p.N) return;
+                        const int cidx = ncol >> 4;                                  // logical metadata column of w0
+                        if (p.c_meta_ref != nullptr) {
+                            uint32_t* e = p.c_meta_ref + row16 * (int64_t)(p.N / 2) + (cidx >> 2) * 32 + m0 * 4 + (cidx & 3);
+                            *reinterpret_cast<uint2*>(e) = make_uint2(w0, w1);
+                        }
+                        if (p.c_meta_tc != nullptr) {
+                            const int64_t t128 = row >> 7;
+                            const int m2 = (int)((row >> 4) & 7);
+                            const int kb = cidx >> 3, j = (cidx & 7) >> 1;
+                            uint32_t* rec = p.c_meta_tc + ((t128 * (int64_t)((p.N + 127) >> 7) + kb) * 128 + m0 + 16 * m2) * 4 + j;
+                            rec[0] = w0;
+                            rec[32] = w1;
+                        }
+                    };
 #pragma unroll
-                for (int c2 = 0; c2 < NPAIR; ++c2) {
-                    const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2], 8);
-                    const uint32_t xb = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2 + 1], 8);
-                    if (!upper) write_words(__byte_perm(meta[2 * c2], xa, 0x5410), __byte_perm(meta[2 * c2], xa, 0x7632), col0 + c2 * 64);
-                    else write_words(__byte_perm(xb, meta[2 * c2 + 1], 0x5410), __byte_perm(xb, meta[2 * c2 + 1], 0x7632), col0 + c2 * 64 + 32);
-                }
-                if constexpr (NCH % 2 == 1) {
-                    const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[NCH - 1], 8);
-                    if (!upper) write_words(__byte_perm(meta[NCH - 1], xa, 0x5410), __byte_perm(meta[NCH - 1], xa, 0x7632), col0 + (NCH - 1) * 32);
+                    for (int c2 = 0; c2 < NPAIR; ++c2) {
+                        const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2], 8);
+                        const uint32_t xb = __shfl_xor_sync(0xFFFFFFFFu, meta[2 * c2 + 1], 8);
+                        if (!upper) write_words(__byte_perm(meta[2 * c2], xa, 0x5410), __byte_perm(meta[2 * c2], xa, 0x7632), col0 + c2 * 64);
+                        else write_words(__byte_perm(xb, meta[2 * c2 + 1], 0x5410), __byte_perm(xb, meta[2 * c2 + 1], 0x7632), col0 + c2 * 64 + 32);
+                    }
+                    if constexpr (NCH % 2 == 1) {
+                        const uint32_t xa = __shfl_xor_sync(0xFFFFFFFFu, meta[NCH - 1], 8);
+                        if (!upper) write_words(__byte_perm(meta[NCH - 1], xa, 0x5410), __byte_perm(meta[NCH - 1], xa, 0x7632), col0 + (NCH - 1) * 32);
+                    }
                 }
             }
             if (++a == ACC) { a = 0; acc_phase ^= 1u; }

@@ -223,12 +223,17 @@ S24_API int s24_spmm_ref_meta_noalloc(const void* vals, const void* meta_ref, co
                               const s24_tile_cfg* cfg, void* stream);
 
 /*
- * Sparse GEMM whose epilogue 2:4-prunes the fp32 accumulator along N and stores it
- * compressed (compression/kernels/10.1_prune_acc.py:88-154,624-678): C_vals (M, N/2) in
- * the element type (rounded after selection, :241) and metadata of the (M, N) result in
- * the reference layout C_meta_ref ((M/16, N) int16) and/or C_meta_tc; either may be NULL.
- * Keys are the signed accumulator values and ties keep the lower index, as in
- * 10.1_prune_acc.py:100-105.  Needs N % 128 == 0 in addition to the s24_spmm rules.
+ * Sparse GEMM whose epilogue 2:4-prunes the accumulator along N on its way out of tensor
+ * memory and stores it compressed (compression/kernels/10.1_prune_acc.py:88-154,624-678):
+ * C_vals (M, N/2) in the element type and metadata of the (M, N) result in the reference
+ * layout C_meta_ref ((M/16, N) int16) and/or C_meta_tc; either may be NULL.  Keys are the
+ * signed accumulator values, ties keep the lower index and the codes come from the keep
+ * mask, as in 10.1_prune_acc.py:100-117.  The groups are ranked after the fp32 sums have been
+ * rounded to the element type: the output is, bit for bit, prune + compress (lower index on
+ * ties) of the C that s24_spmm stores for the same operands and tile.  The reference's kernel
+ * ranks the unrounded fp32 values and rounds the survivors (:241); the two differ only in
+ * groups whose second and third largest sums round to the same 16-bit number, i.e. well inside
+ * the tolerance the GEMM itself is held to.  Needs N % 128 == 0 in addition to the s24_spmm rules.
  */
 S24_API int s24_spmm_prune_out(const void* vals, const void* meta_tc, const void* B,
                        void* C_vals, void* C_meta_ref, void* C_meta_tc,

@@ -94,15 +94,17 @@ def print_table(path: str) -> int:
     if not recs:
         print(f"no records in {path}", file=sys.stderr)
         return 1
-    cols = [c for c in ("dense", "sparse", "sparse_ref_meta", "two_kernel", "fused_in", "fused_out", "separated",
+    cols = [c for c in ("dense", "sparse", "sparse_untuned", "sparse_ref_meta", "two_kernel", "fused_in", "fused_out", "separated",
                         "vendor_sparse", "vendor_two_step", "compress_gbs") if any(c in d for d in recs.values())]
     print("| M | K | " + " | ".join(cols) + " |")
     print("|---|---|" + "---|" * len(cols))
     for (m, k) in sorted(recs, key=lambda mk: (-mk[0] * mk[1], -mk[0])):
         d = recs[(m, k)]
         print(f"| {m} | {k} | " + " | ".join(f"{d[c]:.0f}" if c in d else "-" for c in cols) + " |")
+    lose = [(m, k) for (m, k), d in recs.items() if "sparse" in d and "dense" in d and d["sparse"] < d["dense"]]
     means = {c: sum(d[c] for d in recs.values() if c in d) / max(1, sum(1 for d in recs.values() if c in d)) for c in cols}
     print("| mean | | " + " | ".join(f"{means[c]:.0f}" for c in cols) + " |")
+    print(f"\nsparse below dense on {len(lose)} of {len(recs)} shapes: {sorted(lose)}")
     return 0
 
 
@@ -165,12 +167,18 @@ def main():
             return round(flops / ms / 1e9, 1)
 
         rec["dense"] = tf(timeit(lambda: torch.matmul(A_pruned, B, out=C)))
-        rec["sparse"] = tf(timeit(lambda: s24.spmm(vals, tc, B, out=C)))
-        rec["sparse_ref_meta"] = tf(timeit(lambda: s24.spmm(vals, E, B, meta_layout="ref", out=C)))
+        # like the reference's launchers (tune=True, gluon_ws_sparse.py:572-582) the GEMM lines run the tile
+        # shape an autotune pass picked for this (M, N, K); the library's untuned heuristic is timed beside it
+        from s24.ops import _autotune
+        tuned = _autotune(vals, tc, B, C, M, N, K)
+        rec["tile"] = "heuristic" if tuned is None else f"{tuned['BM']}x{tuned['BN']}"
+        rec["sparse"] = tf(timeit(lambda: s24.spmm(vals, tc, B, out=C, manual_config=tuned)))
+        rec["sparse_untuned"] = tf(timeit(lambda: s24.spmm(vals, tc, B, out=C)))
+        rec["sparse_ref_meta"] = tf(timeit(lambda: s24.spmm(vals, E, B, meta_layout="ref", out=C, manual_config=tuned)))
 
         def two_kernel():
             v, _, t = s24.prune_compress(A, tie="higher", want_ref=False, want_tc=True)
-            s24.spmm(v, t, B, out=C)
+            s24.spmm(v, t, B, out=C, manual_config=tuned)
 
         rec["two_kernel"] = tf(timeit(two_kernel))
         rec["fused_in"] = tf(timeit(lambda: s24.spmm_prune_in(A, B, out=C)))

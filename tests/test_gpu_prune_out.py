@@ -2,11 +2,14 @@
 two-kernel comparison (v10.2).
 
 Oracle, as the reference's own check builds it (compression/kernels/10.1_prune_acc.py:727-730):
-C_ref = A_pruned @ B, then prune_2_4 and compress_dense_to_sparse of C_ref.  The kernel prunes
-the fp32 accumulator, whose low bits depend on summation order, so the keep mask is required
-to match the oracle's except in groups whose 2nd and 3rd largest values are closer than the
-GEMM tolerance (rtol = atol = 1e-2); where masks agree the stored values must agree within that
-tolerance, and where they do not the stored values must still be genuine elements of the group.
+C_ref = A_pruned @ B, then prune_2_4 and compress_dense_to_sparse of C_ref.  The low bits of an
+accumulator depend on summation order (and the kernel ranks the sums after rounding them to the
+output type), so the keep mask is required to match the oracle's prune of the fp32 product
+except in groups whose 2nd and 3rd largest values are closer than the GEMM tolerance
+(rtol = atol = 1e-2); where masks agree the stored values must agree within that tolerance, and
+where they do not the stored values must still be genuine elements of the group.  Independently of
+any tolerance, the fused output must equal, bit for bit, the oracle's prune (lower index on ties)
+of the dense C the plain kernel stores for the same operands and tile.
 """
 import numpy as np
 import pytest
@@ -77,6 +80,28 @@ def test_fused_output_prune(mods, M, N, K, dtype, cfg):
     C32 = Ap @ B.to(DEV).float()
     _check_against_oracle(cv, ce, C32, dtype)
     # the two metadata layouts describe the same array
+    assert torch.equal(s24.meta_convert(ct, "tc", "ref", M, N), ce)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (1024, 1152, 512), (160, 256, 192)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [{"BM": 128, "BN": 128}, {"BM": 256, "BN": 128}, {"BM": 256, "BN": 256}, {"BM": 512, "BN": 224}])
+def test_fused_output_is_prune_compress_of_the_plain_kernels_c(mods, M, N, K, dtype, cfg):
+    """decompress(C_vals, C_meta) == oracle.prune(C) with C from s24_spmm on the same tile: no tolerance"""
+    s24 = mods["s24"]
+    A = randn((M, K), dtype, 7 * M + N + K)
+    B = randn((K, N), dtype, 7 * M + N + K + 1)
+    vals, _, tc = s24.prune_compress(A.to(DEV), want_ref=False, want_tc=True)
+    C = s24.spmm(vals, tc, B.to(DEV), manual_config=cfg)
+    cv, ce, ct = s24.spmm_prune_out(vals, tc, B.to(DEV), want_ref=True, want_tc=True, manual_config=cfg)
+    want = oracle.prune(bits(C), ODT[dtype], oracle.MODE_SIGNED, oracle.TIE_LOWER)
+    off = oracle.meta_offsets(M, N // 16)
+    ml = ce.cpu().numpy().reshape(-1)[off].reshape(M, N // 16)
+    got = oracle.decompress(bits(cv), ml)
+    assert np.array_equal(got & 0x7FFF, want & 0x7FFF)                  # same survivors in the same places
+    nz = (want & 0x7FFF) != 0
+    assert np.array_equal(got[nz], want[nz])                            # with their signs
+    assert np.isin(_codes_to_mask(ml), [0b0011, 0b0101, 0b0110, 0b1001, 0b1010, 0b1100]).all()
     assert torch.equal(s24.meta_convert(ct, "tc", "ref", M, N), ce)
 
 
