@@ -64,7 +64,7 @@ PC_M = PC_K = 16384
 H100_PRECOMPRESSED_SPARSE_8192 = 1015.48   # TFLOP/s, the reference's published number for this metric (H100)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of these exact workloads
 # (summaries under profiles/): the 8192^3 GEMM with its default 512x224 tile, and prune+compress at 16384^2
-NCU_DRAM_BYTES_GEMM_8192 = 560.35e6 + 118.96e6
+NCU_DRAM_BYTES_GEMM_8192 = 571.80e6 + 124.87e6
 NCU_DRAM_BYTES_PC_16384 = 536.91e6 + 267.39e6
 
 
@@ -481,7 +481,7 @@ def run_ours(args, rank, world, local):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin, n_sus = time.time(), 0
     e0.record(stream)
-    while time.time() - t_begin < 2.0:
+    while time.time() - t_begin < args.sustained_seconds:
         for _ in range(100):
             gemm_step()
         n_sus += 100
@@ -785,6 +785,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the back-to-back loop behind the `sustained` record (shorten it for a profiler's launch list)")
     ap.add_argument("--profile-target", choices=["gemm", "prune_compress", "prune_in"], default=None,
                     help="for ncu captures: launch only this kernel (warm-up + --steps launches) and exit")
     ap.add_argument("--size", type=int, default=0, help="with --profile-target: square problem size (default: the bench's)")
@@ -798,7 +800,8 @@ def main():
         # launched without torchrun: re-launch one rank per GPU
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", __file__, "--gpus", str(args.gpus),
-               "--steps", str(args.steps), "--warmup", str(args.warmup)] + (["--no-cpu"] if args.no_cpu else [])
+               "--steps", str(args.steps), "--warmup", str(args.warmup), "--sustained-seconds", str(args.sustained_seconds)]
+        cmd += ["--no-cpu"] if args.no_cpu else []
         return subprocess.call(cmd)
     return run_ours(args, rank, world, local)
 
