@@ -35,7 +35,30 @@ static void run_p(const uint16_t* A, int64_t numel, int tie, uint16_t* out)
     }
 }
 
+// the GEMM epilogue's variant: signed keys, lower index on ties, codes from the keep mask
+template <int DT>
+static void run_pc_mask(const uint16_t* A, int64_t M, int64_t K, uint16_t* vals, uint16_t* meta)
+{
+    for (int64_t r = 0; r < M; ++r)
+        for (int64_t c8 = 0; c8 < K / 8; ++c8) {
+            const uint16_t* a = A + r * K + 8 * c8;
+            uint32_t in[4];
+            for (int i = 0; i < 4; ++i) in[i] = a[2 * i] | ((uint32_t)a[2 * i + 1] << 16);
+            uint32_t lo, hi;
+            uint32_t codes = prune_compress_8_from_mask<DT>(in[0], in[1], in[2], in[3], lo, hi) >> 24;
+            uint16_t* v = vals + r * (K / 2) + 4 * c8;
+            v[0] = lo & 0xFFFF; v[1] = lo >> 16; v[2] = hi & 0xFFFF; v[3] = hi >> 16;
+            uint16_t& w = meta[r * (K / 16) + c8 / 2];
+            if (c8 % 2 == 0) w = (uint16_t)codes; else w |= (uint16_t)(codes << 8);
+        }
+}
+
 extern "C" {
+void host_prune_compress_from_mask(const uint16_t* A, int64_t M, int64_t K, int dtype, uint16_t* vals, uint16_t* meta_logical)
+{
+    if (dtype == kBf16) run_pc_mask<kBf16>(A, M, K, vals, meta_logical);
+    else run_pc_mask<kFp16>(A, M, K, vals, meta_logical);
+}
 void host_prune_compress(const uint16_t* A, int64_t M, int64_t K, int dtype, int mode, int tie,
                          uint16_t* vals, uint16_t* meta_logical)
 {

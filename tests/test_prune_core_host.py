@@ -29,6 +29,7 @@ def host(tmp_path_factory):
     vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
     L.host_prune_compress.argtypes = [vp, i64, i64, i32, i32, i32, vp, vp]
     L.host_prune.argtypes = [vp, i64, i32, i32, i32, vp]
+    L.host_prune_compress_from_mask.argtypes = [vp, i64, i64, i32, vp, vp]
     L.host_keep_mask.argtypes = [vp, i32]
     L.host_keep_mask.restype = ctypes.c_uint
     return L
@@ -132,3 +133,33 @@ def test_random_bits_no_nan(host):
             got_v, got_ml = _pc(host, b, dtype, mode, 0)
             assert np.array_equal(got_v, want_v) and np.array_equal(got_ml, want_ml)
             assert np.array_equal(_p(host, b, dtype, mode, 0), want_p)
+
+
+@pytest.mark.parametrize("dtype,alpha", [(oracle.FP16, F16), (oracle.BF16, BF16)])
+def test_epilogue_variant_encodes_from_the_keep_mask(host, dtype, alpha):
+    """prune_compress_8_from_mask (the GEMM's pruning epilogue): the keep mask is the oracle's signed,
+    lower-index prune, and the codes name the kept positions even where a kept value is an exact zero
+    (compression/kernels/10.1_prune_acc.py:115-117 encodes from its mask)"""
+    rng = np.random.default_rng(5 + dtype)
+    tie_heavy = _alphabet_matrix(np.uint16, [v for k, v in alpha.items()], 64, 256, seed=17 + dtype)
+    rand = rng.integers(0, 65536, size=(64, 256), dtype=np.uint16)
+    expmask = 0x7C00 if dtype == oracle.FP16 else 0x7F80
+    nan = ((rand & expmask) == expmask) & ((rand & (~expmask & 0x7FFF)) != 0)
+    rand[nan] = 0x3C00
+    for a in (tie_heavy, rand):
+        a = np.ascontiguousarray(a)
+        M, K = a.shape
+        vals = np.zeros((M, K // 2), np.uint16)
+        meta = np.zeros((M, K // 16), np.uint16)
+        host.host_prune_compress_from_mask(a.ctypes.data, M, K, dtype, vals.ctypes.data, meta.ctypes.data)
+        _, want_mask = oracle.prune(a, dtype, oracle.MODE_SIGNED, oracle.TIE_LOWER, return_mask=True)
+        w = meta.astype(np.uint32)
+        codes = np.stack([(w >> (4 * j)) & 0xF for j in range(4)], axis=-1).reshape(M, K // 4)
+        idx0, idx1 = codes & 3, codes >> 2
+        assert (idx0 < idx1).all()
+        got_mask = ((1 << idx0) | (1 << idx1)).astype(np.uint8)
+        assert np.array_equal(got_mask, want_mask)
+        groups = a.reshape(M, K // 4, 4)
+        v = vals.reshape(M, K // 4, 2)
+        assert np.array_equal(v[..., 0], np.take_along_axis(groups, idx0[..., None].astype(np.int64), -1)[..., 0])
+        assert np.array_equal(v[..., 1], np.take_along_axis(groups, idx1[..., None].astype(np.int64), -1)[..., 0])
