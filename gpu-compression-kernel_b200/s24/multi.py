@@ -185,6 +185,7 @@ class NShardedSpmm:
         shard of C, or with replicated=True the full (M, n_total) C on every rank (all-gather).
         replicated="copy" gives the same result with the shards pushed by the copy engines, panel by
         panel, while the GEMM of the next panel runs (result buffer owned and reused like "fused").
+        replicated="auto" picks "copy" on two GPUs and "fused" otherwise.
         replicated="fused" gives the same result without a collective on the data path: the GEMM
         itself stores each shard into every rank's copy of C.  That copy is a buffer owned by this
         object and is returned again (overwritten) by the next fused call of the same shape."""
@@ -198,6 +199,11 @@ class NShardedSpmm:
         if n_local * self.world != n_total:
             raise RuntimeError("replicated output needs equal column shards on every rank "
                                f"(N_local={n_local}, world={self.world}, N={n_total})")
+        if replicated == "auto":
+            # measured on cfg 5 (28672 x 8192 x 65536): with two GPUs the GEMM is the longer leg and the
+            # copy engines hide the exchange behind it on the GEMM's best tile; from four GPUs on the link
+            # is the bound and the fused epilogue, which hides the whole GEMM under it, is faster
+            replicated = "copy" if self.world == 2 else "fused"
         if replicated == "fused":
             return self._fused(B_shard, n_total)
         if replicated == "copy":
