@@ -469,13 +469,22 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
                     if (row_ok) {
                         uint16_t* vrow = static_cast<uint16_t*>(p.c_vals) + row * (int64_t)(p.N / 2) + col0 / 2;
+                        // rows of C_vals are N bytes long (N % 128 == 0) and chunks 32 bytes: aligned if the base is
+                        const bool wide_vals = (reinterpret_cast<uintptr_t>(p.c_vals) & 31u) == 0;
 #pragma unroll
                         for (int c = 0; c < NCH; ++c) {
                             if (col0 + c * 32 < p.N) {
-                                *reinterpret_cast<uint4*>(vrow + c * 16) =
-                                    make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
-                                *reinterpret_cast<uint4*>(vrow + c * 16 + 8) =
-                                    make_uint4(vals[c * 8 + 4], vals[c * 8 + 5], vals[c * 8 + 6], vals[c * 8 + 7]);
+                                if (wide_vals) {   // 16 values = 32 bytes = one whole sector per store
+                                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(vrow + c * 16),
+                                                 "r"(vals[c * 8]), "r"(vals[c * 8 + 1]), "r"(vals[c * 8 + 2]), "r"(vals[c * 8 + 3]),
+                                                 "r"(vals[c * 8 + 4]), "r"(vals[c * 8 + 5]), "r"(vals[c * 8 + 6]), "r"(vals[c * 8 + 7])
+                                                 : "memory");
+                                } else {
+                                    *reinterpret_cast<uint4*>(vrow + c * 16) =
+                                        make_uint4(vals[c * 8], vals[c * 8 + 1], vals[c * 8 + 2], vals[c * 8 + 3]);
+                                    *reinterpret_cast<uint4*>(vrow + c * 16 + 8) =
+                                        make_uint4(vals[c * 8 + 4], vals[c * 8 + 5], vals[c * 8 + 6], vals[c * 8 + 7]);
+                                }
                             }
                         }
                     }
