@@ -771,10 +771,12 @@ def run_profile_target(args):
         n = args.size or PC_M
         A = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
         fn = lambda: s24.prune_compress(A, want_ref=True, want_tc=False)  # noqa: E731
-    for _ in range(max(args.warmup, 1) + args.steps):
+    for _ in range(max(args.warmup, 1)):
         fn()
     torch.cuda.synchronize(dev)
-    print(f"profile target {args.profile_target} n={n}: {max(args.warmup, 1) + args.steps} launches done")
+    ms = time_steps(fn, args.steps, torch.cuda.current_stream(dev)) / args.steps
+    print(f"profile target {args.profile_target} n={n}: {max(args.warmup, 1) + args.steps} launches done, "
+          f"{ms * 1e3:.1f} us per launch (CUDA events over the last {args.steps})")
     return 0
 
 

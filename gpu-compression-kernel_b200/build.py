@@ -1,6 +1,6 @@
 """Build libs24.so (the C-ABI CUDA library) in-tree for sm_100a.
 
-    python gpu-compression-kernel_b200/build.py [--force] [--verbose]
+    python gpu-compression-kernel_b200/build.py [--force] [--verbose] [--define NAME=VALUE ...] [--out PATH]
 
 nvcc cross-compiles without a GPU.  The shared object lands next to the Python loader
 (``s24/libs24.so``) so that it travels with the source tree; it links the CUDA runtime
@@ -43,17 +43,21 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines=(), dest: Path = OUT) -> Path:
+    """`defines` (NAME=VALUE strings) and `dest` build a variant library somewhere else, e.g. the
+    timing experiments of csrc/spmm_tcgen05.cu; load it with S24_LIBRARY=<path>."""
+    variant = bool(defines) or Path(dest) != OUT
+    if not variant and not force and not _stale():
         return OUT
     objs = []
-    objdir = HERE / "build"
-    objdir.mkdir(exist_ok=True)
+    objdir = (HERE / "build") if not variant else Path(dest).with_suffix(".objs")
+    objdir.mkdir(parents=True, exist_ok=True)
     srcs = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
     procs = []
     for src in srcs:
         obj = objdir / (src.stem + ".o")
-        cmd = [nvcc(), *NVCC_FLAGS, "-Xptxas", "-v" if verbose else "-O3", "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-Xptxas", "-v" if verbose else "-O3", "-c", str(src),
+               "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
     for src, p in procs:
@@ -63,14 +67,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}")
     link = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
-            "-o", str(OUT), *map(str, objs)]
+            "-o", str(dest), *map(str, objs)]
     subprocess.run(link, check=True)
-    return OUT
+    return Path(dest)
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], metavar="NAME=VALUE", help="extra -D for a variant build")
+    ap.add_argument("--out", default=str(OUT), help="where to put the shared object (default: next to the loader)")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, defines=a.define, dest=Path(a.out)))

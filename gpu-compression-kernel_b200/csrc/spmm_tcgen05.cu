@@ -41,6 +41,13 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 
+// Timing experiments only (never set in a shipped build: the results are wrong).  Bit 0: the
+// plain epilogue hands tensor memory back without reading it; bit 1: no A / metadata loads;
+// bit 2: no B loads.  They size what each part of the pipeline costs (see the profile notes).
+#ifndef S24_TIMING_DIAG
+#define S24_TIMING_DIAG 0
+#endif
+
 // ring depths of the 512 x 224 tile: 7 A units (3.5 k-blocks) and 3 B units fill the 227 KB
 #ifndef S24_NA_224
 #define S24_NA_224 7
@@ -203,10 +210,11 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 auto load_a = [&](int kb, int m) -> bool {
                     if (!mbar_wait(bar_a_empty + 8 * sa, pha ^ 1u, p.wait_limit_ns)) return false;
                     const uint32_t full = (G == 2) ? mapa(bar_a_full + 8 * sa, 0) : (bar_a_full + 8 * sa);
-                    if (leader) mbar_arrive_expect_tx(bar_a_full + 8 * sa, (uint32_t)(G * Cfg::kATxBytes));
+                    if (leader) mbar_arrive_expect_tx(bar_a_full + 8 * sa, (S24_TIMING_DIAG & 2) ? 0u : (uint32_t)(G * Cfg::kATxBytes));
                     const int rows = row0 + m * kRowsPerCta * G;
                     const int rec = (rows / kRowsPerCta) * kblocks + kb;
-                    if (G == 2) {
+                    if (S24_TIMING_DIAG & 2) {
+                    } else if (G == 2) {
                         tma_load_2d_pair(smem_a + sa * Cfg::kASubBytes, &tm_a, kb * 64, rows, full);
                         tma_load_2d_pair(smem_e + sa * Cfg::kESubBytes, &tm_e, 0, rec * 4, full);
                     } else {
@@ -219,9 +227,10 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 auto load_b = [&](int kb) -> bool {
                     if (!mbar_wait(bar_b_empty + 8 * sb, phb ^ 1u, p.wait_limit_ns)) return false;
                     const uint32_t full = (G == 2) ? mapa(bar_b_full + 8 * sb, 0) : (bar_b_full + 8 * sb);
-                    if (leader) mbar_arrive_expect_tx(bar_b_full + 8 * sb, (uint32_t)(G * Cfg::kBLoadBytes));
+                    if (leader) mbar_arrive_expect_tx(bar_b_full + 8 * sb, (S24_TIMING_DIAG & 4) ? 0u : (uint32_t)(G * Cfg::kBLoadBytes));
                     const uint32_t b_dst = smem_b + sb * Cfg::kBBytes;
-                    if constexpr (Cfg::kBT) {
+                    if constexpr ((S24_TIMING_DIAG & 4) != 0) {
+                    } else if constexpr (Cfg::kBT) {
                         // transposed B: two boxes of (64 k-values x kBNCta rows of N)
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
@@ -409,32 +418,37 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     for (int j = 0; j < width / 2; ++j)
                         q[c_off / 2 + j] = pack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), p.bf16);
                 };
-                int done = 0;
+                if constexpr ((S24_TIMING_DIAG & 1) != 0) {   // timing experiment: nothing is read
 #pragma unroll
-                for (int k = 0; k < CW / 128; ++k) {
-                    uint32_t r[128];
-                    tc_ld_32x32b_x128(tacc + (uint32_t)done, r);
-                    tc_wait_ld();
-                    pack(r, done, 128);
-                    done += 128;
-                }
-                if constexpr ((CW % 128) == 96) {
-                    uint32_t r[64], r2[32];
-                    tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
-                    tc_ld_32x32b_x32(tacc + (uint32_t)(done + 64), r2);
-                    tc_wait_ld();
-                    pack(r, done, 64);
-                    pack(r2, done + 64, 32);
-                } else if constexpr ((CW % 128) == 64) {
-                    uint32_t r[64];
-                    tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
-                    tc_wait_ld();
-                    pack(r, done, 64);
-                } else if constexpr ((CW % 128) == 32) {
-                    uint32_t r[32];
-                    tc_ld_32x32b_x32(tacc + (uint32_t)done, r);
-                    tc_wait_ld();
-                    pack(r, done, 32);
+                    for (int j = 0; j < CW / 2; ++j) q[j] = 0u;
+                } else {
+                    int done = 0;
+#pragma unroll
+                    for (int k = 0; k < CW / 128; ++k) {
+                        uint32_t r[128];
+                        tc_ld_32x32b_x128(tacc + (uint32_t)done, r);
+                        tc_wait_ld();
+                        pack(r, done, 128);
+                        done += 128;
+                    }
+                    if constexpr ((CW % 128) == 96) {
+                        uint32_t r[64], r2[32];
+                        tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
+                        tc_ld_32x32b_x32(tacc + (uint32_t)(done + 64), r2);
+                        tc_wait_ld();
+                        pack(r, done, 64);
+                        pack(r2, done + 64, 32);
+                    } else if constexpr ((CW % 128) == 64) {
+                        uint32_t r[64];
+                        tc_ld_32x32b_x64(tacc + (uint32_t)done, r);
+                        tc_wait_ld();
+                        pack(r, done, 64);
+                    } else if constexpr ((CW % 128) == 32) {
+                        uint32_t r[32];
+                        tc_ld_32x32b_x32(tacc + (uint32_t)done, r);
+                        tc_wait_ld();
+                        pack(r, done, 32);
+                    }
                 }
                 // every accumulator column of this warp has been read: hand TMEM back to the MMA warp
                 tc_fence_before();

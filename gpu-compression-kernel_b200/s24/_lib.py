@@ -4,8 +4,11 @@ from __future__ import annotations
 import ctypes
 from pathlib import Path
 
+import os
+
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libs24.so"
+# S24_LIBRARY=<path> loads another build of the library (a variant made with build.py --define ... --out ...)
+LIB_PATH = Path(os.environ["S24_LIBRARY"]) if os.environ.get("S24_LIBRARY") else _HERE / "libs24.so"
 
 OK = 0
 ERR_INVALID_ARG, ERR_SHAPE, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = -1, -2, -3, -4, -5
