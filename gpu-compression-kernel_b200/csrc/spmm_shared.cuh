@@ -12,7 +12,10 @@ namespace s24 {
 
 constexpr int kBlockK = 128;        // logical K per pipeline stage
 constexpr int kRowsPerCta = 128;
-constexpr int kGroupM = 8;          // M-tiles per raster group (compression/common.py:155)
+#ifndef S24_GROUP_M
+#define S24_GROUP_M 8
+#endif
+constexpr int kGroupM = S24_GROUP_M;   // M-tiles per raster group (compression/common.py:155)
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {
