@@ -72,3 +72,33 @@ def test_cpu_tensors_are_rejected_loudly(built):
         s24.prune(torch.zeros(4, 8, dtype=torch.float16))
     with pytest.raises(ValueError):
         s24.prune(torch.zeros(4, 6, dtype=torch.float16))
+
+
+def test_more_argument_errors_need_no_gpu(built):
+    """entry points added for the multi-GPU and self-test paths validate before touching CUDA too"""
+    from s24 import _lib
+    L = _lib.lib()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert L.s24_peer_copy_2d(None, 64, p, 64, 32, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.s24_peer_copy_2d(p, 16, p, 64, 32, 4, None) == _lib.ERR_SHAPE           # pitch smaller than the width
+    assert L.s24_peer_copy_2d(p, 64, p, 64, 0, 4, None) == _lib.OK                   # nothing to copy
+    assert L.s24_selftest_timeout(5, None, None, None, None, 0, 0, 0, 0, None, None) == _lib.ERR_INVALID_ARG
+    assert L.s24_selftest_timeout(1, p, p, p, p, 128, 128, 128, 0, None, None) == _lib.ERR_SHAPE   # needs two k-blocks
+    # shapes of the reference-layout entry points are checked before their scratch is sized
+    assert L.s24_spmm_ref_meta_noalloc(p, p, p, p, 1 << 40, 128, 1 << 40, 128, 128, 0, None, None) == _lib.ERR_SHAPE
+    assert L.s24_spmm_ref_meta_noalloc(p, p, p, p, 16384, 128, 16384, 128, 128, 0, None, None) == _lib.ERR_SHAPE
+    assert "built-in buffer" in _lib.last_error()
+
+
+def test_library_path_can_be_overridden(built, tmp_path):
+    """S24_LIBRARY=<path> loads another build of the library (variant builds of build.py --define ... --out ...)"""
+    import shutil
+    import subprocess
+    other = tmp_path / "libs24_copy.so"
+    shutil.copy(built, other)
+    code = ("import sys; sys.path.insert(0, %r); from s24 import _lib; "
+            "assert str(_lib.LIB_PATH) == %r, _lib.LIB_PATH; assert _lib.lib().s24_version() == 1; print('ok')" % (str(PKG), str(other)))
+    import os
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, S24_LIBRARY=str(other)), capture_output=True, text=True)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
