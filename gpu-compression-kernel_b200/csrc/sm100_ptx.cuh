@@ -158,6 +158,13 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 
 // ---------------------------------------------------------------- TMA (tensor) loads, no multicast
 
+// bring a tensor map (a __grid_constant__ kernel parameter) into the descriptor cache before the
+// first copy that uses it, so that copy does not wait for the 128-byte descriptor fetch
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 // CTA-local form: data and barrier in the issuing CTA
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
 {

@@ -125,6 +125,7 @@ spmm_prune_in_kernel(const __grid_constant__ CUtensorMap tm_b, const PruneInPara
         mbar_init(bar_acc_empty, kEpiWarps * G);
         *abort_flag = 0;
         fence_barrier_init();
+        prefetch_tensormap(&tm_b);   // the descriptor fetch overlaps the rest of the set-up
     }
     if (warp == 1) {
         tmem_alloc<G>(tmem_slot, kTmemCols);

@@ -182,6 +182,12 @@ spmm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         *abort_flag = 0;
         fence_barrier_init();
     }
+    if (warp == 0 && lane == 0) {   // descriptor fetches overlap the set-up below
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+        if (Cfg::kBTailCols != 0 && !Cfg::kBT) prefetch_tensormap(&tm_b_tail);
+        prefetch_tensormap(&tm_e);
+    }
     if (warp == 1) {
         tmem_alloc<G>(tmem_slot, kTmemCols);
         tmem_relinquish<G>();
