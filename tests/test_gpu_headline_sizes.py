@@ -79,6 +79,28 @@ def test_sparse_gemm_8192_cubed_normal_data(mods, cfg_8192, cfg):
         _check_panel(C[r0:r0 + 128], _panel_reference(d["ap"], r0, d["B"], torch.float16))
 
 
+def test_sparse_gemm_and_fused_output_8192_cubed_bf16(mods):
+    """the same workload in bf16 (the dtype of cfg 5): plain product on sampled panels against the
+    oracle-pruned operand, and the pruning epilogue bit for bit against the oracle's prune of that C"""
+    s24 = mods["s24"]
+    M = K = N = 8192
+    A = randn((M, K), torch.bfloat16, 4002)
+    B = randn((K, N), torch.bfloat16, 4003).to(DEV)
+    ap = oracle.prune(bits(A), oracle.BF16)
+    vals, ml, e = oracle.compress(ap, oracle.BF16)
+    v, E = from_bits(vals, torch.bfloat16, DEV), torch.from_numpy(e).to(DEV).view(M // 16, K)
+    C = mods["ws"].run_sparse_ws_matmul(v, E, B, tune=False)
+    cv, ce = mods["v101"].run_sparse_ws_matmul(v, E, B, tune=False)
+    _status_ok()
+    off = oracle.meta_offsets(128, N // 16)
+    for r0 in (0, 3968, 8064):
+        _check_panel(C[r0:r0 + 128], _panel_reference(ap, r0, B, torch.bfloat16))
+        want = oracle.prune(bits(C[r0:r0 + 128]), oracle.BF16, oracle.MODE_SIGNED, oracle.TIE_LOWER)
+        got_ml = ce[r0 // 16:(r0 + 128) // 16].cpu().numpy().reshape(-1)[off].reshape(128, N // 16)
+        got = oracle.decompress(bits(cv[r0:r0 + 128]), got_ml)
+        assert np.array_equal(got & 0x7FFF, want & 0x7FFF)
+
+
 def _codes_to_mask(meta_logical: np.ndarray) -> np.ndarray:
     w = meta_logical.view(np.uint16).astype(np.uint32)
     codes = np.stack([(w >> (4 * j)) & 0xF for j in range(4)], axis=-1).reshape(w.shape[0], -1)
