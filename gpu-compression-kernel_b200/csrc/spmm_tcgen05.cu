@@ -14,23 +14,23 @@
 //     holds units of one 128-row sub-tile x one k-block of 128 (A values: 128 rows x 64 values,
 //     128-byte swizzle, plus the 2 KB metadata record), the B ring units of one k-block of this
 //     CTA's part of B (128 rows x BN_CTA columns as 64-column swizzled atoms).  A k-block
-//     consumes MT units of A and one of B; separate rings let a sub-tile's A unit go back to the
-//     producer as soon as its own MMAs are done and keep more bytes in flight than whole
-//     (A + B) stages of the same total size would;
+//     consumes MT units of A and one of B; with separate rings a sub-tile's A unit goes back to
+//     the producer as soon as its own MMAs are done;
 //   * warp 1: MMA issuer (one elected lane).  Per k-block and sub-tile: tcgen05.cp moves the
 //     metadata record into 4 TMEM columns, then four tcgen05.mma.sp (K = 32 each) accumulate
 //     into TMEM; tcgen05.commit releases the A unit, after the last sub-tile the B unit and,
 //     after the last k-block, publishes that sub-tile's accumulator;
 //   * warps 2-9: epilogue, two warps per 32-lane TMEM quadrant (they split the tile's columns,
-//     or take one row sub-tile each).  One accumulator row per thread: wide tcgen05.ld
-//     (128 / 64 / 32 columns per round trip), convert, 32-byte stores issued as the data
-//     arrives, then TMEM is handed back to the MMA warp;
+//     or take one row sub-tile each, which has accumulator barriers of its own).  One
+//     accumulator row per thread: wide tcgen05.ld (128, then 64 + 32 columns per round trip),
+//     round to 16 bits in registers, hand TMEM back to the MMA warp, then 32-byte stores (or,
+//     in the pruning epilogue, rank the rounded values and store them compressed);
 //   * CTA pairs (cta_group::2): each CTA loads its own 128 rows of A and half of the B
 //     tile (no multicast), the leader CTA issues 256-row MMAs that read both CTAs' shared
 //     memory, completion is multicast to both CTAs' barriers.  Only the leader's producer
 //     arrives on the "full" barrier (with the byte count of both CTAs); the peer's copies
 //     complete on that barrier without an arrive of their own;
-//   * optionally (MT = 2) a pair owns two 256-row sub-tiles that share every B stage.
+//   * optionally (MT = 2) a pair owns two 256-row sub-tiles that share every B unit.
 // Every barrier wait is bounded; on a timeout the kernel records a code in the status word
 // (see s24_device_status), frees its tensor memory and returns.
 #include "s24_common.cuh"
