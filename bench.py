@@ -761,6 +761,12 @@ def run_profile_target(args):
         vals, _, tc = s24.prune_compress(A, want_ref=False, want_tc=True)
         C = torch.empty(n, n, dtype=torch.float16, device=dev)
         fn = lambda: s24.spmm(vals, tc, B, out=C)  # noqa: E731
+    elif args.profile_target == "fused_out":
+        n = args.size or GEMM_M
+        A = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+        B = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+        vals, _, tc = s24.prune_compress(A, want_ref=False, want_tc=True)
+        fn = lambda: s24.spmm_prune_out(vals, tc, B, want_ref=True, want_tc=False)  # noqa: E731
     elif args.profile_target == "prune_in":
         n = args.size or 4096
         A = torch.randn(n, n, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
@@ -789,7 +795,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="length of the back-to-back loop behind the `sustained` record (shorten it for a profiler's launch list)")
-    ap.add_argument("--profile-target", choices=["gemm", "prune_compress", "prune_in"], default=None,
+    ap.add_argument("--profile-target", choices=["gemm", "fused_out", "prune_compress", "prune_in"], default=None,
                     help="for ncu captures: launch only this kernel (warm-up + --steps launches) and exit")
     ap.add_argument("--size", type=int, default=0, help="with --profile-target: square problem size (default: the bench's)")
     args = ap.parse_args()
