@@ -102,3 +102,15 @@ def test_library_path_can_be_overridden(built, tmp_path):
     import os
     r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, S24_LIBRARY=str(other)), capture_output=True, text=True)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+def test_a_c_program_binds_the_library(built, tmp_path):
+    """gcc compiles tests/host/abi_smoke.c against include/s24.h, links libs24.so and runs it: the
+    boundary is plain C (no C++ types, no torch), and its argument validation needs no GPU"""
+    import subprocess
+    exe = tmp_path / "abi_smoke"
+    libdir = built.parent
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", f"-I{ROOT / 'include'}", str(ROOT / "tests/host/abi_smoke.c"),
+                    "-o", str(exe), f"-L{libdir}", "-ls24", f"-Wl,-rpath,{libdir}"], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "abi smoke ok" in r.stdout, r.stdout + r.stderr
