@@ -1,7 +1,9 @@
-"""Drop-in for the reference's compression/compress_2_4.py (16-bit element types).
+"""Drop-in for the reference's compression/compress_2_4.py.
 
 `compress_dense_to_sparse` keeps the reference's signature, return shapes, metadata
-layout and error behaviour and runs on the B200 through libs24 (C ABI `s24_compress`).
+layout and error behaviour and runs on the B200 through libs24 (C ABI `s24_compress` for
+fp16 / bf16, the types the sparse GEMM consumes; `s24_compress_other` for the int8, int32 and
+float32 branches).
 """
 import torch
 
@@ -31,9 +33,9 @@ def compress_dense_to_sparse(dense):
     (m/16, k) (compression/gluon_ws_sparse.py:656)."""
     if dense.dim() != 2:
         raise RuntimeError(f"Expected 2-dimensional dense tensor, got {dense.dim()}-dimensional tensor")
+    if dense.dtype in (torch.int8, torch.float, torch.int32):   # compress_2_4.py:41-47,73-76,144-154
+        return s24.compress_other(dense)
     if dense.dtype not in (torch.half, torch.bfloat16):
-        if dense.dtype in (torch.int8, torch.float, torch.int32):
-            raise RuntimeError(f"Datatype {dense.dtype} is not supported by the B200 library (fp16 / bf16 only)")
         raise RuntimeError(f"Invalid datatype {dense.dtype} of dense matrix")
     m, k = dense.shape
     if m % 32 != 0:

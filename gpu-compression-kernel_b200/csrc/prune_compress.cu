@@ -215,6 +215,65 @@ __global__ void __launch_bounds__(256) meta_ref_tc_kernel(const uint2* __restric
     }
 }
 
+// ---------------------------------------------------------------- compress, other element types
+
+// compress_dense_to_sparse for the element types beyond fp16 / bf16 (compression/compress_2_4.py:41-47
+// metadata type, :73-76 the 1:2 float branch, :144-154 eight codes per int32 word).  None of the
+// reference's GEMM launchers consumes these, so this is a plain one-thread-per-metadata-word kernel:
+// the thread reads the CODES groups of its word with 16-byte loads, applies the reference's flag
+// logic (:113-121), stores the kept values and writes the word at its reordered place (:20-28).
+//   T = int8_t : 2:4, 8 codes per int32 word (32 elements per thread)
+//   T = int32_t: 2:4, 4 codes per int16 word (16 elements per thread)
+//   T = float  : 1:2, a pair (e0, e1) counts as the group (e0, e0, e1, e1); 4 codes per int16 word
+template <typename T, int KSPARSE, int CODES, typename META>
+__global__ void __launch_bounds__(256) compress_other_kernel(const T* __restrict__ dense, int64_t ld, int64_t M, int64_t ncols,
+                                                             T* __restrict__ vals, META* __restrict__ meta)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= M * ncols) return;
+    const int64_t r = idx / ncols, c = idx - r * ncols;
+    constexpr int ELEMS = KSPARSE * CODES;          // elements of this thread's word
+    constexpr int VEC = 16 / (int)sizeof(T);        // elements per 16-byte load
+    __align__(16) T in[ELEMS];
+    const T* src = dense + r * ld + c * ELEMS;
+#pragma unroll
+    for (int v = 0; v < ELEMS / VEC; ++v)
+        *reinterpret_cast<uint4*>(in + v * VEC) = *reinterpret_cast<const uint4*>(src + v * VEC);
+    __align__(16) T out[ELEMS / 2];
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < CODES; ++j) {
+        const T* g = in + j * KSPARSE;
+        bool m0, m1, m3;
+        if (KSPARSE == 4) {
+            m0 = g[0] != T(0); m1 = g[1] != T(0); m3 = g[3] != T(0);
+        } else {
+            m0 = m1 = g[0] != T(0);
+            m3 = g[1] != T(0);
+        }
+        const bool expr0 = m0 && m1, expr1 = !m0 && m1, expr2 = !m0 && !m1;
+        const int idx0 = (int)expr1 | ((int)expr2 << 1);
+        const int idx1 = (int)(expr0 || expr2 || m3) | ((int)(expr1 || !m1) << 1);
+        if (KSPARSE == 4) {
+            out[2 * j] = g[idx0];
+            out[2 * j + 1] = g[idx1];
+        } else {
+            out[j] = g[idx0 >> 1];
+        }
+        word |= (uint32_t)(idx0 | (idx1 << 2)) << (4 * j);
+    }
+    T* dst = vals + r * (ncols * (ELEMS / 2)) + c * (ELEMS / 2);
+    constexpr int OUT_BYTES = (ELEMS / 2) * (int)sizeof(T);
+    if (OUT_BYTES >= 16) {
+#pragma unroll
+        for (int v = 0; v < OUT_BYTES / 16; ++v) *reinterpret_cast<uint4*>(dst + v * VEC) = *reinterpret_cast<const uint4*>(out + v * VEC);
+    } else {
+#pragma unroll
+        for (int v = 0; v < ELEMS / 2; ++v) dst[v] = out[v];
+    }
+    meta[meta_index(S24_META_REF, r, c, ncols)] = (META)word;
+}
+
 // ---------------------------------------------------------------- gathered shards -> row-major
 
 // An all-gather of column shards arrives shard-major, (G, rows, nl); the caller wants (rows, G*nl).
@@ -307,6 +366,43 @@ extern "C" int s24_compress(const void* dense, int64_t M, int64_t K, int64_t ld,
 {
     return launch_prune_compress(dense, M, K, ld, dtype, kModeNone, kTieLower, vals, meta_ref, meta_tc,
                                  static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int s24_compress_other(const void* dense, int64_t M, int64_t K, int64_t ld, int elem_type, void* vals,
+                                  void* meta_ref, void* stream)
+{
+    if (dense == nullptr || vals == nullptr || meta_ref == nullptr) return fail(S24_ERR_INVALID_ARG, "compress_other: null pointer");
+    if (elem_type != S24_INT8 && elem_type != S24_INT32 && elem_type != S24_FP32)
+        return fail(S24_ERR_INVALID_ARG, "compress_other: element type %d (S24_INT8, S24_INT32 or S24_FP32 expected)", elem_type);
+    const int codes = elem_type == S24_INT8 ? 8 : 4;
+    const int ksparse = elem_type == S24_FP32 ? 2 : 4;
+    const int row_mult = elem_type == S24_INT8 ? 16 : 32;
+    const int64_t esize = elem_type == S24_INT8 ? 1 : 4;
+    if (M < 0 || K < 0) return fail(S24_ERR_SHAPE, "compress_other: negative shape");
+    if (M % row_mult != 0) return fail(S24_ERR_SHAPE, "Number of rows of dense matrix %lld must be divisible by %d", (long long)M, row_mult);
+    if (K % (4 * codes) != 0)
+        return fail(S24_ERR_SHAPE, "Number of columns of dense matrix %lld must be divisible by %d", (long long)K, 4 * codes);
+    const int64_t ncols = K / (ksparse * codes);
+    if (ncols % 4 != 0)
+        return fail(S24_ERR_SHAPE, "The number of metadata cols must be at least 4, current number: %lld", (long long)ncols);
+    if (ld < K || (ld * esize) % 16 != 0) return fail(S24_ERR_SHAPE, "compress_other: row stride %lld must be >= K and a multiple of 16 bytes", (long long)ld);
+    if (!aligned(dense, 16) || !aligned(vals, 16) || !aligned(meta_ref, 4))
+        return fail(S24_ERR_INVALID_ARG, "compress_other: dense and vals must be 16-byte aligned");
+    if (M == 0 || K == 0) return S24_OK;
+    const int64_t words = M * ncols;
+    const int64_t blocks = (words + 255) / 256;
+    if (blocks > 0x7FFFFFFF) return fail(S24_ERR_SHAPE, "compress_other: matrix too large for one launch");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (elem_type == S24_INT8)
+        compress_other_kernel<int8_t, 4, 8, int32_t><<<(unsigned)blocks, 256, 0, s>>>(
+            static_cast<const int8_t*>(dense), ld, M, ncols, static_cast<int8_t*>(vals), static_cast<int32_t*>(meta_ref));
+    else if (elem_type == S24_INT32)
+        compress_other_kernel<int32_t, 4, 4, int16_t><<<(unsigned)blocks, 256, 0, s>>>(
+            static_cast<const int32_t*>(dense), ld, M, ncols, static_cast<int32_t*>(vals), static_cast<int16_t*>(meta_ref));
+    else
+        compress_other_kernel<float, 2, 4, int16_t><<<(unsigned)blocks, 256, 0, s>>>(
+            static_cast<const float*>(dense), ld, M, ncols, static_cast<float*>(vals), static_cast<int16_t*>(meta_ref));
+    return check_cuda(cudaGetLastError(), "compress_other launch");
 }
 
 extern "C" int s24_prune(const void* A, void* out, int64_t numel, int dtype, int mode, int tie, void* stream)

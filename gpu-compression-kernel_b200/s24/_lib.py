@@ -13,6 +13,7 @@ LIB_PATH = Path(os.environ["S24_LIBRARY"]) if os.environ.get("S24_LIBRARY") else
 OK = 0
 ERR_INVALID_ARG, ERR_SHAPE, ERR_CUDA, ERR_UNSUPPORTED, ERR_TIMEOUT = -1, -2, -3, -4, -5
 FP16, BF16 = 0, 1
+INT8, INT32, FP32 = 2, 3, 4
 MODE_SIGNED, MODE_MAGNITUDE = 0, 1
 TIE_REFERENCE, TIE_LOWER, TIE_HIGHER = 0, 1, 2
 META_LOGICAL, META_REF, META_TC = 0, 1, 2
@@ -32,6 +33,7 @@ SIGNATURES = {
     "s24_last_error": (ctypes.c_char_p, []),
     "s24_prune": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp]),
     "s24_compress": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
+    "s24_compress_other": (_i32, [_vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp]),
     "s24_prune_compress": (_i32, [_vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "s24_meta_tc_bytes": (_sz, [_i64, _i64]),
     "s24_meta_convert": (_i32, [_vp, _i32, _vp, _i32, _i64, _i64, _vp]),

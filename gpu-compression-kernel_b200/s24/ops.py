@@ -152,6 +152,39 @@ def compress(dense: torch.Tensor, want_ref: bool = True, want_tc: bool = False):
     return vals, e, tc
 
 
+_OTHER = {torch.int8: (L.INT8, torch.int32, 16, 8, 4), torch.int32: (L.INT32, torch.int16, 32, 4, 4),
+          torch.float32: (L.FP32, torch.int16, 32, 4, 2)}   # code, metadata type, row multiple, codes per word, group size
+
+
+def compress_other(dense: torch.Tensor):
+    """compress_dense_to_sparse for int8 / int32 / float32 input (compression/compress_2_4.py:41-47,73-76,
+    144-154): returns (values (M, K/2), reordered metadata viewed (M/2, 2 * words per row)), with the
+    reference's exception types for the shapes it rejects."""
+    if dense.dim() != 2:
+        raise RuntimeError(f"Expected 2-dimensional dense tensor, got {dense.dim()}-dimensional tensor")
+    if dense.dtype not in _OTHER:
+        raise RuntimeError(f"Invalid datatype {dense.dtype} of dense matrix")
+    code, meta_dtype, row_mult, codes, ksparse = _OTHER[dense.dtype]
+    m, k = dense.shape
+    if m % row_mult != 0:
+        raise RuntimeError(f"Number of rows of dense matrix {m} must be divisible by {row_mult}")
+    if k % (4 * codes) != 0:
+        raise RuntimeError(f"Number of columns of dense matrix {k} must be divisible by {4 * codes}")
+    if m * k == 0:
+        return dense, torch.zeros(dense.shape, dtype=meta_dtype, device=dense.device)
+    ncols = k // (ksparse * codes)
+    assert ncols % 4 == 0, f"The number of metadata cols must be at least 4, current number: {ncols}"
+    _require_cuda(dense)
+    d = dense
+    if d.stride(1) != 1 or (d.stride(0) * d.element_size()) % 16 != 0 or d.stride(0) < k or d.data_ptr() % 16 != 0:
+        d = d.contiguous()
+    vals = torch.empty((m, k // 2), dtype=dense.dtype, device=dense.device)
+    meta = torch.empty((m * ncols,), dtype=meta_dtype, device=dense.device)
+    with _on_device(dense):
+        L.check(L.lib().s24_compress_other(_p(d), m, k, d.stride(0), code, _p(vals), _p(meta), _stream(dense)))
+    return vals, meta.view(-1, 2 * ncols)
+
+
 def prune_compress(A: torch.Tensor, mode: str = "signed", tie: str = "reference", want_ref: bool = True,
                    want_tc: bool = False):
     """Fused prune + compress, one pass over A (kernels/11.1_2_kernel_baseline.py:171-203,256-279).

@@ -23,7 +23,8 @@
  * reference project (paths relative to its root):
  *
  *   s24_prune            compression/prune.py:57-96           prune_2_4
- *   s24_compress         compression/compress_2_4.py:32-161   compress_dense_to_sparse
+ *   s24_compress         compression/compress_2_4.py:32-161   compress_dense_to_sparse (fp16 / bf16)
+ *   s24_compress_other   same function, its int8 / int32 / float32 branches
  *   s24_prune_compress   compression/kernels/11.1_2_kernel_baseline.py:171-203,256-279
  *                                                             ws_tma_compress_2_4_kernel
  *   s24_meta_convert     compression/compress_2_4.py:6-30     _calculate_meta_reordering_offsets
@@ -82,6 +83,10 @@ extern "C" {
 /* element types */
 #define S24_FP16 0
 #define S24_BF16 1
+/* accepted by s24_compress_other only */
+#define S24_INT8 2
+#define S24_INT32 3
+#define S24_FP32 4
 
 /* which keys rank the four elements of a group */
 #define S24_MODE_SIGNED 0          /* the values themselves: prune.py:85 (reference default) */
@@ -135,6 +140,21 @@ S24_API int s24_prune(const void* A, void* out, int64_t numel, int dtype, int mo
  */
 S24_API int s24_compress(const void* dense, int64_t M, int64_t K, int64_t ld, int dtype,
                  void* vals, void* meta_ref, void* meta_tc, void* stream);
+
+/*
+ * compress_dense_to_sparse for its element types beyond fp16 / bf16
+ * (compression/compress_2_4.py:41-47,73-76,144-154), which no GEMM of the reference consumes:
+ *   S24_INT8   2:4, metadata int32 with eight codes per word; M % 16 == 0, K % 32 == 0
+ *   S24_INT32  2:4, metadata int16 with four codes per word;  M % 32 == 0, K % 16 == 0
+ *   S24_FP32   1:2 (of every pair the first element if it is non-zero, else the second; codes 0100 /
+ *              1110), metadata int16; M % 32 == 0, K % 16 == 0
+ * and a number of metadata words per row that is a multiple of 4 (compress_2_4.py:10).  vals is
+ * (M, K/2) of the element type, meta_ref the reordered metadata buffer of M * words-per-row
+ * elements (the reference returns it viewed (M/2, 2 * words-per-row)).  dense has row stride ld
+ * elements (a multiple of 16 bytes); dense and vals 16-byte aligned.
+ */
+S24_API int s24_compress_other(const void* dense, int64_t M, int64_t K, int64_t ld, int elem_type,
+                       void* vals, void* meta_ref, void* stream);
 
 /*
  * Fused prune + compress in one pass over A (the reference's standalone kernel,

@@ -51,6 +51,8 @@ def lib() -> ctypes.CDLL:
         L.s24o_prune_f32.restype = i32
         L.s24o_compress.argtypes = [vp, i64, i64, i32, vp, vp, vp]
         L.s24o_compress.restype = i32
+        L.s24o_compress_other.argtypes = [vp, i64, i64, i32, vp, vp]
+        L.s24o_compress_other.restype = i32
         L.s24o_prune_compress.argtypes = [vp, i64, i64, i32, i32, i32, vp, vp, vp, vp]
         L.s24o_prune_compress.restype = i32
         L.s24o_meta_offsets.argtypes = [i64, i64, vp]
@@ -141,6 +143,34 @@ def compress(dense_bits: np.ndarray, dtype: int = FP16):
     rc = lib().s24o_compress(_p(d), M, K, dtype, _p(vals), _p(ml), _p(mr))
     assert rc == 0
     return vals, ml, mr
+
+
+_OTHER_KIND = {np.dtype(np.int8): 0, np.dtype(np.int32): 1, np.dtype(np.float32): 2}
+
+
+def compress_other(dense: np.ndarray):
+    """``compress_dense_to_sparse`` for int8 / int32 / float32 input (compress_2_4.py:41-47,73-76,144-154).
+
+    Returns (vals (M, K/2) of the input type, meta): meta is the reordered buffer viewed
+    (M/2, 2 * ncols) like the reference returns it, int32 for int8 input, else int16.
+    Raises RuntimeError / AssertionError for the conditions the reference rejects."""
+    d = np.ascontiguousarray(dense)
+    kind = _OTHER_KIND[d.dtype]
+    M, K = d.shape
+    rows = 16 if kind == 0 else 32
+    cols = 32 if kind == 0 else 16
+    if M % rows != 0:
+        raise RuntimeError(f"Number of rows of dense matrix {M} must be divisible by {rows}")
+    if K % cols != 0:
+        raise RuntimeError(f"Number of columns of dense matrix {K} must be divisible by {cols}")
+    ncols = K // (32 if kind == 0 else (8 if kind == 2 else 16))
+    if ncols % 4 != 0:
+        raise AssertionError(f"The number of metadata cols must be at least 4, current number: {ncols}")
+    vals = np.empty((M, K // 2), dtype=d.dtype)
+    meta = np.empty((M * ncols,), dtype=np.int32 if kind == 0 else np.int16)
+    rc = lib().s24o_compress_other(_p(d), M, K, kind, _p(vals), _p(meta))
+    assert rc == 0, rc
+    return vals, meta.reshape(-1, 2 * ncols)
 
 
 def prune_compress(a_bits: np.ndarray, dtype: int = FP16, mode: int = MODE_SIGNED, tie: int = TIE_REFERENCE):

@@ -130,6 +130,37 @@ def test_input_is_not_modified_and_strided_rows_work(mods):
     assert np.array_equal(bits(v), want_v) and np.array_equal(e.cpu().numpy(), want_e)
 
 
+@pytest.mark.parametrize("name,dtype", [("int8", torch.int8), ("int32", torch.int32), ("float32", torch.float32)])
+def test_other_element_types_of_compress(mods, name, dtype):
+    """compress_dense_to_sparse for int8 / int32 / float32 (compress_2_4.py:41-47,73-76,144-154) through the
+    drop-in: the reference's golden outputs, then larger random patterns and a strided view against the oracle"""
+    from pathlib import Path
+    c = mods["compress"].compress_dense_to_sparse
+    g = dict(np.load(Path(__file__).resolve().parent / "golden" / "golden_other_dtypes.npz"))
+    v, m = c(torch.from_numpy(g[f"{name}.dense"]).to(DEV))
+    assert v.dtype == dtype and tuple(m.shape) == g[f"{name}.meta"].shape
+    assert np.array_equal(v.cpu().numpy().view(np.uint8), g[f"{name}.vals"].view(np.uint8))
+    assert np.array_equal(m.cpu().numpy(), g[f"{name}.meta"])
+    rng = np.random.default_rng(7)
+    for (M, K) in ((512, 1024), (96 if dtype != torch.int8 else 80, 2176)):
+        flags = rng.integers(0, 2, size=(M, K))
+        dense = (flags * rng.integers(-50, 50, size=(M, K))).astype(g[f"{name}.dense"].dtype)
+        want_v, want_m = oracle.compress_other(dense)
+        wide = torch.zeros(M, K + 64, dtype=dtype, device=DEV)
+        wide[:, 32:32 + K] = torch.from_numpy(dense).to(DEV)
+        for src in (torch.from_numpy(dense).to(DEV), wide[:, 32:32 + K]):         # contiguous, then row stride > K
+            v, m = c(src)
+            assert np.array_equal(v.cpu().numpy().view(np.uint8), want_v.view(np.uint8))
+            assert np.array_equal(m.cpu().numpy(), want_m)
+    with pytest.raises(RuntimeError, match="divisible by"):
+        c(torch.zeros(24, 128, dtype=dtype, device=DEV))
+    with pytest.raises(AssertionError):
+        c(torch.zeros(32, 32 if dtype == torch.int8 else 16, dtype=dtype, device=DEV))
+    d = torch.zeros(0, 128, dtype=dtype, device=DEV)
+    v, m = c(d)
+    assert v.shape == d.shape and m.numel() == 0 and m.dtype == (torch.int32 if dtype == torch.int8 else torch.int16)
+
+
 def test_error_behaviour_matches_reference(mods):
     c = mods["compress"].compress_dense_to_sparse
     with pytest.raises(ValueError):
@@ -144,6 +175,8 @@ def test_error_behaviour_matches_reference(mods):
         c(torch.zeros(32, 48, dtype=torch.float16, device=DEV))
     with pytest.raises(RuntimeError, match="Invalid datatype"):
         c(torch.zeros(32, 64, dtype=torch.float64, device=DEV))
+    with pytest.raises(RuntimeError, match="Invalid datatype"):
+        c(torch.zeros(32, 64, dtype=torch.int64, device=DEV))
     # empty input: returned as is with zero metadata (compress_2_4.py:67)
     d = torch.zeros(0, 64, dtype=torch.float16, device=DEV)
     v, m = c(d)

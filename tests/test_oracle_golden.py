@@ -126,3 +126,28 @@ def test_error_behaviour():
         oracle.compress(np.zeros((32, 40), dtype=np.uint16))
     with pytest.raises(AssertionError):
         oracle.compress(np.zeros((32, 48), dtype=np.uint16))
+
+
+@pytest.mark.parametrize("name", ["int8", "int32", "float32"])
+def test_other_element_types_match_the_reference(name):
+    """compress_dense_to_sparse's int8 / int32 / float32 branches (compress_2_4.py:41-47,73-76,144-154):
+    the oracle against outputs of the reference's own function (tests/golden/make_golden_other_dtypes.py)"""
+    import numpy as np
+    from pathlib import Path
+    g = dict(np.load(Path(__file__).resolve().parent / "golden" / "golden_other_dtypes.npz"))
+    vals, meta = oracle.compress_other(g[f"{name}.dense"])
+    assert vals.dtype == g[f"{name}.vals"].dtype and meta.dtype == g[f"{name}.meta"].dtype
+    assert np.array_equal(vals.view(np.uint8), g[f"{name}.vals"].view(np.uint8))      # bit patterns, -0.0 included
+    assert np.array_equal(meta, g[f"{name}.meta"])
+
+
+def test_other_element_types_reject_what_the_reference_rejects():
+    import numpy as np
+    with pytest.raises(RuntimeError, match="divisible by 16"):
+        oracle.compress_other(np.zeros((8, 128), np.int8))
+    with pytest.raises(RuntimeError, match="divisible by 32"):
+        oracle.compress_other(np.zeros((16, 48), np.int8))
+    with pytest.raises(RuntimeError, match="divisible by 32"):
+        oracle.compress_other(np.zeros((16, 64), np.float32))
+    with pytest.raises(AssertionError):
+        oracle.compress_other(np.zeros((32, 16), np.float32))     # 2 metadata columns
