@@ -316,6 +316,24 @@ def leg_prune_compress(dev, stream, peaks):
             rec["cold_l2"] = {"ms": ms_c, "gbs": bytes_pc / (ms_c * 1e-3) / 1e9,
                               "note": "single launches, each after writing a 256 MiB buffer; event overhead included"}
         out[name] = rec
+        if n == PC_M and dtype == torch.float16:
+            # prune_2_4 alone (dense in, dense out: 4 bytes per element), the a1 row of the path
+            po = torch.empty_like(Ap)
+
+            def prune_step():
+                sp = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+                _lib.check(L.s24_prune(ctypes.c_void_p(Ap.data_ptr()), ctypes.c_void_p(po.data_ptr()), n * n, code,
+                                       _lib.MODE_SIGNED, _lib.TIE_REFERENCE, sp))
+
+            for _ in range(5):
+                prune_step()
+            torch.cuda.synchronize(dev)
+            ms_p = time_steps(prune_step, 20, stream) / 20
+            gbs_p = 4.0 * n * n / (ms_p * 1e-3) / 1e9
+            out["prune_dense_fp16_%d" % n] = {"metric": "prune_2_4_gbs", "value": gbs_p, "unit": "GB/s", "ms": ms_p,
+                                              "workload": f"prune_2_4 fp16 {n}x{n} -> dense pruned tensor (2 bytes read + 2 written per element)",
+                                              "roofline": hbm_roofline(gbs_p, 4.0 * n * n, peaks)}
+            del po
         del Ap, pv, pe
     del flush
     return out
